@@ -1,0 +1,254 @@
+/* tessl_b200: the MLX affine-quantized matmul path of bharathvbcr/tessl for NVIDIA B200.
+ *
+ * A C ABI in the conventions of the reference's `src/capi.rs`: an opaque,
+ * thread-affine runtime handle, an `int32_t` status with the message written
+ * NUL-terminated into a caller buffer (`err` may be NULL), every argument
+ * validated before any GPU work, and each call returning with the runtime
+ * idle unless encode-only mode is on.
+ *
+ * Each operator entry below replaces one function of the reference's typed
+ * kernel API (`src/nn.rs`, `src/qwen35_q4.rs`); the citation names the file
+ * and lines of the reference project it mirrors. Argument order follows the
+ * Rust signature. A `GpuBuffer` becomes a `TesslBuf`: a device pointer plus
+ * its capacity in bytes, which the library checks against what a kernel will
+ * read or write exactly as `nn::require` does (src/nn.rs:126-143).
+ */
+#ifndef TESSL_B200_H
+#define TESSL_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#if defined(__GNUC__)
+#define TESSL_API __attribute__((visibility("default")))
+#else
+#define TESSL_API
+#endif
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Status codes (src/capi.rs:78-80). */
+#define TESSL_OK 0
+#define TESSL_ERR 1
+#define TESSL_PANIC 2
+
+/* Bumped on any change to a struct layout or a signature below; bindings
+ * refuse a library whose version differs (src/capi.rs:82-91). */
+#define TESSL_B200_ABI_VERSION 1u
+
+/* Largest M of the small-batch kernel (src/nn.rs:4524). */
+#define TESSL_GEMM_Q4_MLX_MAX_M 8u
+
+typedef struct TesslRuntime TesslRuntime;
+
+/* Device memory handed to an operator: pointer and capacity in bytes. */
+typedef struct TesslBuf {
+    void *ptr;
+    uint64_t nbytes;
+} TesslBuf;
+
+/* src/nn.rs:3238-3245. */
+typedef struct TesslQuantShape {
+    uint32_t rows;       /* output rows N */
+    uint32_t cols;       /* reduction length K */
+    uint32_t group_size; /* weights per (scale, bias) pair; must divide cols */
+} TesslQuantShape;
+
+/* src/nn.rs:3332-3338: packed nibbles (two per byte, low first = MLX's
+ * little-endian U32 words) and one bf16 (scale, bias) pair per group. */
+typedef struct TesslQ4MlxBank {
+    TesslBuf packed;
+    TesslBuf scales_biases;
+} TesslQ4MlxBank;
+
+/* src/nn.rs:3669-3675. Only the row-major layout is built; Interleaved4 (an
+ * Apple-GPU repack no Qwen3.5 path uses) is refused by name. */
+#define TESSL_Q4_ROW_MAJOR 0u
+#define TESSL_Q4_INTERLEAVED4 1u
+
+/* src/nn.rs:4408-4415. */
+typedef struct TesslQkvOutputs {
+    TesslBuf q_out;
+    TesslBuf k_out;
+    TesslBuf v_out;
+} TesslQkvOutputs;
+
+/* ------------------------------------------------------------- runtime --- */
+
+/* src/capi.rs:186-189. */
+TESSL_API uint32_t tessl_abi_version(void);
+
+/* A runtime on the calling thread's current CUDA device, with a stream of its
+ * own; NULL with the reason in `err` on failure (src/capi.rs:255-276). */
+TESSL_API TesslRuntime *tessl_runtime_new(char *err, size_t err_len);
+
+/* The same on a named device ordinal. No counterpart in the reference, which
+ * has one system default device; multi-GPU hosts need to choose. */
+TESSL_API TesslRuntime *tessl_runtime_new_on_device(int32_t device, char *err, size_t err_len);
+
+/* Free on the creating thread; NULL is ignored; a foreign thread leaks the
+ * handle and gets TESSL_ERR (src/capi.rs:278-293). */
+TESSL_API int32_t tessl_runtime_free(TesslRuntime *rt);
+
+/* Wait for all submitted work (src/capi.rs:295-303). */
+TESSL_API int32_t tessl_synchronize(TesslRuntime *rt, char *err, size_t err_len);
+
+/* Accepted for signature compatibility (src/capi.rs:305-332): `on` must be 0
+ * or 1. Every call here is already a single submission that is waited for once,
+ * which is what the reference's async-encode mode gives; the mode changes
+ * nothing a caller can observe. */
+TESSL_API int32_t tessl_runtime_set_async_encode(TesslRuntime *rt, uint32_t on, char *err, size_t err_len);
+
+/* Encode-only mode: operators enqueue their kernels on the runtime's stream
+ * and return without waiting, the contract of the Rust `nn::*` functions
+ * themselves (src/lib.rs:96-106), for callers that batch a whole token's
+ * projections and wait once with tessl_synchronize. Off by default. */
+TESSL_API int32_t tessl_runtime_set_encode_only(TesslRuntime *rt, uint32_t on, char *err, size_t err_len);
+
+/* 1 when a CUDA fault has latched the runtime (every later call is refused),
+ * else 0; works on a poisoned runtime (src/capi.rs:212-247). */
+TESSL_API int32_t tessl_runtime_poisoned(TesslRuntime *rt, int32_t *out, char *err, size_t err_len);
+
+/* Kernels launched since the last call, then reset to zero: lets a caller
+ * prove a refused call did no GPU work (`take_dispatch_count`,
+ * tests/gemm_q4_mlx_tensorops.rs:374 in the reference project). */
+TESSL_API int32_t tessl_runtime_take_dispatch_count(TesslRuntime *rt, uint64_t *out, char *err, size_t err_len);
+
+/* The runtime's CUDA stream (a `cudaStream_t`) and device ordinal, so a caller
+ * can order its own work or record events around operator calls. */
+TESSL_API void *tessl_runtime_stream(TesslRuntime *rt);
+TESSL_API int32_t tessl_runtime_device(TesslRuntime *rt);
+
+/* Test hook: latch the poison flag without a GPU fault (the reference's
+ * `poison_as_shared_event_timeout_for_test`, src/runtime.rs:1076). */
+TESSL_API int32_t tessl_runtime_poison_for_test(TesslRuntime *rt);
+
+/* Device buffers (`GpuRuntime::alloc_buffer`, `GpuBuffer::write_bytes`,
+ * `read_*`; src/runtime.rs:2083, src/tensor.rs). Copies are ordered on the
+ * runtime's stream and complete before return. */
+TESSL_API int32_t tessl_buffer_alloc(TesslRuntime *rt, uint64_t nbytes, TesslBuf *out, char *err, size_t err_len);
+TESSL_API int32_t tessl_buffer_free(TesslRuntime *rt, TesslBuf buf, char *err, size_t err_len);
+TESSL_API int32_t tessl_buffer_write(TesslRuntime *rt, TesslBuf dst, uint64_t dst_offset, const void *src, uint64_t nbytes,
+                           char *err, size_t err_len);
+TESSL_API int32_t tessl_buffer_read(TesslRuntime *rt, TesslBuf src, uint64_t src_offset, void *dst, uint64_t nbytes,
+                          char *err, size_t err_len);
+
+/* ---------------------------------------------------------- Q4 GEMV (M=1) --- */
+
+/* `nn::simd_gemv_threadgroups` (src/nn.rs:3699-3701): ceil(rows / 8). Kept so
+ * callers that reason about the reference's grid partition still can; this
+ * library sizes its own grids. */
+TESSL_API uint64_t tessl_simd_gemv_threadgroups(uint32_t rows);
+
+/* `nn::gemv_q4_mlx_simd` (src/nn.rs:3982-4074): y[rows] = W x (+ resid), x bf16
+ * [cols], y f32 [rows], resid f32 [rows] or NULL; resid may be y itself. */
+TESSL_API int32_t tessl_gemv_q4_mlx_simd(TesslRuntime *rt, TesslQ4MlxBank bank, TesslBuf x_bf16, TesslBuf y,
+                               TesslQuantShape shape, uint32_t layout, const TesslBuf *resid, char *err,
+                               size_t err_len);
+
+/* The same with y stored as bf16 (round to nearest even of the f32 result).
+ * No counterpart in the reference, whose GEMVs always store f32; provided for
+ * callers that keep activations in bf16. resid stays f32. */
+TESSL_API int32_t tessl_gemv_q4_mlx_simd_bf16(TesslRuntime *rt, TesslQ4MlxBank bank, TesslBuf x_bf16, TesslBuf y_bf16,
+                                    TesslQuantShape shape, uint32_t layout, const TesslBuf *resid, char *err,
+                                    size_t err_len);
+
+/* `nn::gemv_q4_mlx_gate_up_silu` (src/nn.rs:4165-4194): mid[rows] =
+ * silu(W_gate x) * (W_up x) in one launch; mid is bf16 when mid_as_bf16 != 0,
+ * else f32. */
+TESSL_API int32_t tessl_gemv_q4_mlx_gate_up_silu(TesslRuntime *rt, TesslQ4MlxBank gate, TesslQ4MlxBank up, TesslBuf x_bf16,
+                                       TesslBuf mid, TesslQuantShape shape, uint32_t mid_as_bf16, char *err,
+                                       size_t err_len);
+
+/* `nn::gemv_q4_mlx_gate_up_gelu` with `GateUpDispatch::Simd(layout)`
+ * (src/nn.rs:4098-4155): the same with tanh-approximate GELU. */
+TESSL_API int32_t tessl_gemv_q4_mlx_gate_up_gelu(TesslRuntime *rt, TesslQ4MlxBank gate, TesslQ4MlxBank up, TesslBuf x_bf16,
+                                       TesslBuf mid, TesslQuantShape shape, uint32_t layout, uint32_t mid_as_bf16,
+                                       char *err, size_t err_len);
+
+/* `nn::gemv_q4_mlx_kv` (src/nn.rs:4279-4351): k_out = W_k x and v_out = W_v x
+ * in one launch; both banks share `shape`. */
+TESSL_API int32_t tessl_gemv_q4_mlx_kv(TesslRuntime *rt, TesslQ4MlxBank k, TesslQ4MlxBank v, TesslBuf x_bf16, TesslBuf k_out,
+                             TesslBuf v_out, TesslQuantShape shape, uint32_t layout, char *err, size_t err_len);
+
+/* `nn::gemv_q4_mlx_qkv` (src/nn.rs:4366-4515): three projections of one x in
+ * one launch; Q has rows_q rows, K and V rows_kv. */
+TESSL_API int32_t tessl_gemv_q4_mlx_qkv(TesslRuntime *rt, TesslQ4MlxBank q, TesslQ4MlxBank k, TesslQ4MlxBank v,
+                              TesslBuf x_bf16, TesslQkvOutputs out, uint32_t rows_q, uint32_t rows_kv, uint32_t cols,
+                              uint32_t group_size, uint32_t layout, char *err, size_t err_len);
+
+/* `qwen35::swiglu` as `Qwen35Model::gate_up_silu` uses it when the fused
+ * kernel is off (src/qwen35_model.rs:1938-1957): out[i] = silu(gate[i]) * up[i]
+ * over n f32 values, out f32 or bf16. The fused entry above is bit-identical
+ * to two tessl_gemv_q4_mlx_simd calls followed by this. */
+TESSL_API int32_t tessl_swiglu(TesslRuntime *rt, TesslBuf gate, TesslBuf up, TesslBuf out, uint32_t n, uint32_t out_as_bf16,
+                     char *err, size_t err_len);
+
+/* ------------------------------------------------- Q4 GEMM, small and large M --- */
+
+/* `nn::gemm_q4_mlx` (src/nn.rs:4535-4619): Y[m, rows] = X[m, cols] W^T
+ * (+ resid) for m <= 8; X bf16 row-major, Y and resid f32 [m, rows]. */
+TESSL_API int32_t tessl_gemm_q4_mlx(TesslRuntime *rt, TesslQ4MlxBank bank, TesslBuf x_bf16, TesslBuf y, TesslQuantShape shape,
+                          uint32_t m, uint32_t layout, const TesslBuf *resid, char *err, size_t err_len);
+
+/* bf16-output twin of tessl_gemm_q4_mlx (no counterpart in the reference). */
+TESSL_API int32_t tessl_gemm_q4_mlx_bf16(TesslRuntime *rt, TesslQ4MlxBank bank, TesslBuf x_bf16, TesslBuf y_bf16,
+                               TesslQuantShape shape, uint32_t m, uint32_t layout, const TesslBuf *resid, char *err,
+                               size_t err_len);
+
+/* `nn::gemm_q4_mlx_tensorops_max_k` (src/nn.rs:4650-4655). */
+TESSL_API uint32_t tessl_gemm_q4_mlx_tensorops_max_k(uint32_t m, uint32_t n, uint32_t group_size);
+
+/* `nn::gemm_q4_mlx_tensorops` (src/nn.rs:4683-4757): the prefill GEMM for any
+ * m, group_size in {32, 64, 128}, row-major bank, no residual; Y f32 [m, rows].
+ * Runs on the tcgen05 tensor cores. */
+TESSL_API int32_t tessl_gemm_q4_mlx_tensorops(TesslRuntime *rt, TesslQ4MlxBank bank, TesslBuf x_bf16, TesslBuf y,
+                                    TesslQuantShape shape, uint32_t m, char *err, size_t err_len);
+
+/* bf16-output twin of tessl_gemm_q4_mlx_tensorops (no counterpart in the reference). */
+TESSL_API int32_t tessl_gemm_q4_mlx_tensorops_bf16(TesslRuntime *rt, TesslQ4MlxBank bank, TesslBuf x_bf16, TesslBuf y_bf16,
+                                         TesslQuantShape shape, uint32_t m, char *err, size_t err_len);
+
+/* `Q4Weight::matmul` (src/qwen35_q4.rs:518-561): the M-dispatch policy over one
+ * bank of group size 64. m == 0 is a no-op, 1 the GEMV, 2..=8 the small-batch
+ * kernel, more the tensor-core GEMM (which refuses a residual). x is bf16
+ * [m, cols], y f32 [m, rows]. */
+TESSL_API int32_t tessl_q4_weight_matmul(TesslRuntime *rt, TesslQ4MlxBank bank, uint32_t rows, uint32_t cols, TesslBuf x_bf16,
+                               uint32_t m, TesslBuf y, const TesslBuf *resid, char *err, size_t err_len);
+
+/* `Q4Weight::gate_up_silu` (src/qwen35_q4.rs:568-611): one row, group 64. */
+TESSL_API int32_t tessl_q4_weight_gate_up_silu(TesslRuntime *rt, TesslQ4MlxBank gate, TesslQ4MlxBank up, uint32_t rows,
+                                     uint32_t cols, TesslBuf x_bf16, TesslBuf mid, uint32_t mid_as_bf16, char *err,
+                                     size_t err_len);
+
+/* ------------------------------------------------------------------- Q8 --- */
+
+/* `nn::gemv_q8` (src/nn.rs:716-795): y[rows] = W x, W signed int8 row-major,
+ * f32 scales and zeros per group, w = scale * (q - zero), f32 x, f32 y. */
+TESSL_API int32_t tessl_gemv_q8(TesslRuntime *rt, TesslBuf packed, TesslBuf scales, TesslBuf zeros, TesslBuf x, TesslBuf y,
+                      uint32_t rows, uint32_t cols, uint32_t group_size, char *err, size_t err_len);
+
+/* MLX-layout 8-bit GEMV/GEMM for m <= 8: unsigned codes 0..255 (four per
+ * little-endian U32), bf16 (scale, bias) pairs, w = scale * code + bias, X bf16
+ * [m, cols]; Y f32 [m, rows], or bf16 when y_as_bf16 != 0. No counterpart in the
+ * reference (its only Q8 kernel is tessl_gemv_q8's); this is the Q4 bank
+ * convention at eight bits. group_size in {32, 64, 128, 256, 512}. */
+TESSL_API int32_t tessl_gemm_q8_mlx(TesslRuntime *rt, TesslBuf codes, TesslBuf scales_biases, TesslBuf x_bf16, TesslBuf y,
+                          TesslQuantShape shape, uint32_t m, uint32_t y_as_bf16, char *err, size_t err_len);
+
+/* ------------------------------------------------------- parity helpers --- */
+
+/* Debug kernels for the bit-exact parity gates: the bank's nibbles as one
+ * byte each [rows, cols], and its dense f32 image w = scale * q + bias
+ * (separate multiply and add) [rows, cols]. */
+TESSL_API int32_t tessl_q4_mlx_unpack(TesslRuntime *rt, TesslQ4MlxBank bank, TesslQuantShape shape, TesslBuf out_u8, char *err,
+                            size_t err_len);
+TESSL_API int32_t tessl_q4_mlx_dequant(TesslRuntime *rt, TesslQ4MlxBank bank, TesslQuantShape shape, TesslBuf out_f32,
+                             char *err, size_t err_len);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TESSL_B200_H */

@@ -1,0 +1,238 @@
+// Runtime handle and host-side validation helpers shared by the operator files.
+//
+// The handle is the thin CUDA analogue of the reference's `GpuRuntime`
+// (src/runtime.rs): a device ordinal, one stream, a poison latch, a launch
+// counter and a growable scratch allocation. The helpers restate the refusal
+// rules of `src/nn.rs` (`require`, `require_disjoint_writes`, `QuantShape::validate`,
+// `Q4MlxBank::validate`) with the same wording, so a caller switching libraries
+// sees the same messages.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <cstdio>
+#include <string>
+#include <thread>
+
+#include "../../include/tessl_b200.h"
+
+namespace tessl {
+
+/// Empty string = Ok(()); anything else is the Err(String) message.
+using Result = std::string;
+inline Result ok() { return std::string(); }
+
+template <typename... A>
+inline std::string fmt(const char *f, A... a)
+{
+    char buf[768];
+    std::snprintf(buf, sizeof buf, f, a...);
+    return std::string(buf);
+}
+
+}  // namespace tessl
+
+struct TesslRuntime {
+    int device = 0;
+    cudaStream_t stream = nullptr;
+    std::thread::id owner;
+    bool poisoned = false;
+    bool async_encode = false;
+    bool encode_only = false;
+    uint64_t dispatch_count = 0;
+    int sm_count = 148;
+    // Scratch for kernels that need global memory beyond their operands
+    // (split-K partial sums, the prefill GEMM's converted activations). Grown on
+    // demand, never shrunk, freed with the handle.
+    void *scratch = nullptr;
+    size_t scratch_bytes = 0;
+    void *tensormap_encode = nullptr;  // cuTensorMapEncodeTiled, resolved lazily
+    // One word of pinned host memory a kernel writes (through its device
+    // alias) when a bounded wait inside it gives up. Checked at every wait.
+    volatile uint32_t *status_host = nullptr;
+    uint32_t *status_dev = nullptr;
+};
+
+namespace tessl {
+
+/// Latches the poison flag on a CUDA error and turns it into a message.
+inline Result cuda_check(TesslRuntime *rt, cudaError_t e, const char *what)
+{
+    if (e == cudaSuccess) return ok();
+    if (rt) rt->poisoned = true;
+    return fmt("%s: CUDA error %d (%s); the runtime is poisoned and must be recreated", what, (int)e,
+               cudaGetErrorString(e));
+}
+
+/// Scratch of at least `bytes`, 256-byte aligned. Growing waits for the stream
+/// (earlier kernels may still read the old allocation) and reallocates.
+inline Result scratch_reserve(TesslRuntime *rt, size_t bytes, void **out)
+{
+    if (bytes > rt->scratch_bytes) {
+        Result r = cuda_check(rt, cudaStreamSynchronize(rt->stream), "scratch_reserve: synchronize");
+        if (!r.empty()) return r;
+        if (rt->scratch) cudaFree(rt->scratch);
+        rt->scratch = nullptr;
+        rt->scratch_bytes = 0;
+        size_t want = (bytes + (size_t(1) << 20) - 1) & ~((size_t(1) << 20) - 1);
+        cudaError_t e = cudaMalloc(&rt->scratch, want);
+        if (e != cudaSuccess) {
+            cudaGetLastError();
+            return fmt("scratch_reserve: cannot allocate %zu bytes of scratch (%s)", want, cudaGetErrorString(e));
+        }
+        rt->scratch_bytes = want;
+    }
+    *out = rt->scratch;
+    return ok();
+}
+
+// ------------------------------------------------------------ validation ---
+
+inline uint64_t elems(uint32_t a, uint32_t b) { return uint64_t(a) * uint64_t(b); }
+
+/// `nn::require::<T>` (src/nn.rs:126-143): capacity in elements of `elem` bytes.
+inline Result require(const TesslBuf &buf, uint64_t need, size_t elem, const std::string &what)
+{
+    const uint64_t have = buf.nbytes / elem;
+    if (have < need) {
+        return fmt("%s: buffer holds %llu elements, kernel reads/writes %llu", what.c_str(),
+                   (unsigned long long)have, (unsigned long long)need);
+    }
+    if (need > 0 && buf.ptr == nullptr) return fmt("%s: null device pointer", what.c_str());
+    return ok();
+}
+
+inline bool aliases(const TesslBuf &a, const TesslBuf &b)
+{
+    if (!a.ptr || !b.ptr || a.nbytes == 0 || b.nbytes == 0) return false;
+    const uintptr_t a0 = (uintptr_t)a.ptr, a1 = a0 + a.nbytes, b0 = (uintptr_t)b.ptr, b1 = b0 + b.nbytes;
+    return a0 < b1 && b0 < a1;
+}
+
+struct Named {
+    const char *name;
+    const TesslBuf *buf;
+};
+
+/// `nn::require_disjoint_writes` (src/nn.rs:146-187): no writable buffer may
+/// overlap another writable buffer or any read-only one.
+inline Result require_disjoint_writes(const char *entry, const Named *writes, int nw, const Named *reads, int nr)
+{
+    for (int i = 0; i < nw; ++i) {
+        for (int j = i + 1; j < nw; ++j) {
+            if (aliases(*writes[i].buf, *writes[j].buf))
+                return fmt("%s: writable buffers %s and %s overlap", entry, writes[i].name, writes[j].name);
+        }
+        for (int j = 0; j < nr; ++j) {
+            if (aliases(*writes[i].buf, *reads[j].buf))
+                return fmt("%s: writable buffer %s overlaps read-only buffer %s", entry, writes[i].name,
+                           reads[j].name);
+        }
+    }
+    return ok();
+}
+
+/// `QuantShape::validate` (src/nn.rs:3254-3267).
+inline Result quant_shape_validate(const TesslQuantShape &s, const std::string &what)
+{
+    if (s.group_size == 0) return fmt("%s: group_size must be non-zero", what.c_str());
+    if (s.cols % s.group_size != 0) {
+        return fmt("%s: cols %u is not a multiple of group_size %u; the kernels compute `cols / group_size` "
+                   "with integer division and would silently drop the ragged tail group",
+                   what.c_str(), s.cols, s.group_size);
+    }
+    return ok();
+}
+
+/// `Q4MlxBank::validate` for a row-major bank (src/nn.rs:3348-3385).
+inline Result q4_bank_validate(const TesslQ4MlxBank &bank, const TesslQuantShape &s, const std::string &what)
+{
+    Result r = quant_shape_validate(s, what);
+    if (!r.empty()) return r;
+    if (s.group_size % 32 != 0 || 512 % s.group_size != 0) {
+        return fmt("%s: group_size %u is outside the MLX kernel domain {32, 64, 128, 256, 512}; the row kernels "
+                   "peel each group through 16-byte loads and the simdgroup kernels stride their scale pointer "
+                   "by 512 / group_size",
+                   what.c_str(), s.group_size);
+    }
+    const uint64_t groups = elems(s.rows, s.cols / s.group_size);
+    const uint64_t weights = elems(s.rows, s.cols);
+    r = require(bank.packed, (weights + 1) / 2, 1, what + " packed");
+    if (!r.empty()) return r;
+    return require(bank.scales_biases, groups, 4, what + " scales_biases (bfloat2 per group)");
+}
+
+/// The kernels read packed rows and activations with 16-byte loads; CUDA
+/// allocations are 256-byte aligned, so only a caller-made sub-view can trip this.
+inline Result require_aligned16(const TesslBuf &b, const std::string &what)
+{
+    if (((uintptr_t)b.ptr & 15u) != 0) return fmt("%s: device pointer must be 16-byte aligned", what.c_str());
+    return ok();
+}
+
+inline Result refuse_layout(uint32_t layout, const char *entry)
+{
+    if (layout == TESSL_Q4_ROW_MAJOR) return ok();
+    if (layout == TESSL_Q4_INTERLEAVED4)
+        return fmt("%s: the Interleaved4 layout is an Apple-GPU repack that this library does not build; "
+                   "pass row-major banks", entry);
+    return fmt("%s: unknown layout %u", entry, layout);
+}
+
+/// `gemm::require_i32_extent` (src/gemm.rs:34-39).
+inline Result require_i32_extent(uint64_t numel, const char *what)
+{
+    if (numel > 0x7fffffffull) return fmt("%s exceeds signed 32-bit kernel indexing", what);
+    return ok();
+}
+
+#define TESSL_TRY(expr)                   \
+    do {                                  \
+        ::tessl::Result _r = (expr);      \
+        if (!_r.empty()) return _r;       \
+    } while (0)
+
+// ----------------------------------------------------- operator prototypes ---
+// The host-side mirror of the reference's `nn::*` functions: validate, then
+// launch on rt->stream. They only enqueue; waiting is the C ABI layer's job.
+namespace nn {
+
+enum OutKind : int { OUT_F32 = 0, OUT_BF16 = 1 };
+
+Result gemv_q4_mlx_simd(TesslRuntime *rt, const TesslQ4MlxBank &bank, const TesslBuf &x_bf16, const TesslBuf &y,
+                        const TesslQuantShape &shape, uint32_t layout, const TesslBuf *resid, OutKind out);
+Result gemv_q4_mlx_gate_up(TesslRuntime *rt, const char *entry, const char *what, bool silu,
+                           const TesslQ4MlxBank &gate, const TesslQ4MlxBank &up, const TesslBuf &x,
+                           const TesslBuf &mid, const TesslQuantShape &shape, uint32_t layout, bool mid_as_bf16);
+Result gemv_q4_mlx_kv(TesslRuntime *rt, const TesslQ4MlxBank &k, const TesslQ4MlxBank &v, const TesslBuf &x_bf16,
+                      const TesslBuf &k_out, const TesslBuf &v_out, const TesslQuantShape &shape, uint32_t layout);
+Result gemv_q4_mlx_qkv(TesslRuntime *rt, const TesslQ4MlxBank &q, const TesslQ4MlxBank &k, const TesslQ4MlxBank &v,
+                       const TesslBuf &x_bf16, const TesslQkvOutputs &out, uint32_t rows_q, uint32_t rows_kv,
+                       uint32_t cols, uint32_t group_size, uint32_t layout);
+Result swiglu(TesslRuntime *rt, const TesslBuf &gate, const TesslBuf &up, const TesslBuf &out, uint32_t n,
+              bool out_as_bf16);
+Result gemm_q4_mlx(TesslRuntime *rt, const TesslQ4MlxBank &bank, const TesslBuf &x_bf16, const TesslBuf &y,
+                   const TesslQuantShape &shape, uint32_t m, uint32_t layout, const TesslBuf *resid, OutKind out);
+uint32_t gemm_q4_mlx_tensorops_max_k(uint32_t m, uint32_t n, uint32_t group_size);
+Result gemm_q4_mlx_tensorops(TesslRuntime *rt, const TesslQ4MlxBank &bank, const TesslBuf &x_bf16,
+                             const TesslBuf &y, const TesslQuantShape &shape, uint32_t m, OutKind out);
+Result gemv_q8(TesslRuntime *rt, const TesslBuf &packed, const TesslBuf &scales, const TesslBuf &zeros,
+               const TesslBuf &x, const TesslBuf &y, uint32_t rows, uint32_t cols, uint32_t group_size);
+Result gemm_q8_mlx(TesslRuntime *rt, const TesslBuf &codes, const TesslBuf &sb, const TesslBuf &x_bf16,
+                   const TesslBuf &y, const TesslQuantShape &shape, uint32_t m, OutKind out);
+Result q4_mlx_unpack(TesslRuntime *rt, const TesslQ4MlxBank &bank, const TesslQuantShape &shape, const TesslBuf &out);
+Result q4_mlx_dequant(TesslRuntime *rt, const TesslQ4MlxBank &bank, const TesslQuantShape &shape,
+                      const TesslBuf &out);
+
+}  // namespace nn
+
+/// `Q4Weight::{matmul, gate_up_silu}` (src/qwen35_q4.rs:518-611).
+namespace q4_weight {
+Result matmul(TesslRuntime *rt, const TesslQ4MlxBank &bank, uint32_t rows, uint32_t cols, const TesslBuf &x_bf16,
+              uint32_t m, const TesslBuf &y, const TesslBuf *resid);
+Result gate_up_silu(TesslRuntime *rt, const TesslQ4MlxBank &gate, const TesslQ4MlxBank &up, uint32_t rows,
+                    uint32_t cols, const TesslBuf &x_bf16, const TesslBuf &mid, bool mid_as_bf16);
+}  // namespace q4_weight
+
+}  // namespace tessl
