@@ -2,248 +2,22 @@
 // host-side wrappers that mirror the reference's `nn::gemv_q4_mlx_*` and
 // `nn::gemm_q4_mlx` (src/nn.rs:3982-4619 of the reference project).
 //
-// The work is a memory-bound stream of the packed weights, so the kernel is
-// organised around bytes in flight, not arithmetic:
-//
-//   * a block owns R consecutive output rows of one bank and its warps split K
-//     into 1024-column chunks (warp w takes chunks w, w + W, ...), so the block
-//     as a whole reads R complete, contiguous packed rows;
-//   * a lane reads 16 bytes (32 nibbles, at most one quantization group) per
-//     row and chunk with a non-allocating 128-bit load, and issues the loads of
-//     all R rows before it touches any of them;
-//   * the lane's 32 activations are widened to f32 registers once per chunk and
-//     reused by all R rows;
-//   * nibbles become floats without an integer-to-float conversion: a byte
-//     permute drops each one into the mantissa of 128.0f, the dot product runs
-//     on 128 + q, and the 128 * sum(x) excess is removed once per 32 weights;
-//   * per lane the group's affine is applied as scale * dot + bias * sum(x) in
-//     f32 (the reference's `qdot16`, kernels/q4_mlx_dot.h:72-94), lanes are
-//     combined by shuffles, warps through shared memory in a fixed order.
-//
-// A row's summation order depends only on `cols`, never on which bank, launch
-// or epilogue it belongs to, so the fused gate/up, K/V and Q/K/V launches are
-// bit-identical to separate launches, as in the reference
-// (kernels/gemv_q4_mlx.metal:634-655).
-#include "q4_common.cuh"
+// The kernel itself (and the reasoning behind its shape) is in
+// q4_gemv_kernel.cuh / q4_gemv_main.cuh; this file holds the host wrappers:
+// validation in the reference's order and wording, the choice of instantiation,
+// the launch.
+#include "q4_gemv_main.cuh"
 #include "runtime.h"
 
 namespace tessl {
 namespace {
 
-enum : int { EPI_STORE = 0, EPI_ADD_RESID = 1, EPI_GATE_UP_GELU = 2, EPI_GATE_UP_SILU = 3 };
-
-struct Q4Seg {
-    const uint8_t *packed0;
-    const uint32_t *sb0;
-    const uint8_t *packed1;  // second bank of a gate/up launch
-    const uint32_t *sb1;
-    void *out;
-    const float *resid;
-    uint32_t rows;
-    uint32_t block_begin;  // first block of this bank within the grid
-};
-
-struct Q4GemvParams {
-    Q4Seg seg[3];
-    int nseg;
-    const uint16_t *x;  // bf16 [m, cols]
-    uint32_t cols;
-    uint32_t group_shift;  // log2(group_size)
-    int epi;
-    int out_bf16;
-};
-
-constexpr int kChunk = 1024;  // columns one warp covers per step: 32 lanes x 32 nibbles
-
-/// sum_i xs[i] * (128 + q_i) over the 32 nibbles of `w`, two chains.
-__device__ __forceinline__ float dot32_biased(const uint4 &w, const float (&xs)[32])
-{
-    const uint32_t words[4] = {w.x, w.y, w.z, w.w};
-    float d0 = 0.0f, d1 = 0.0f;
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-        const uint32_t lo = words[j] & 0x0f0f0f0fu;         // nibbles 0, 2, 4, 6
-        const uint32_t hi = (words[j] >> 4) & 0x0f0f0f0fu;  // nibbles 1, 3, 5, 7
-        d0 = fmaf(xs[8 * j + 0], dev::nib_byte_to_f128<0>(lo), d0);
-        d1 = fmaf(xs[8 * j + 1], dev::nib_byte_to_f128<0>(hi), d1);
-        d0 = fmaf(xs[8 * j + 2], dev::nib_byte_to_f128<1>(lo), d0);
-        d1 = fmaf(xs[8 * j + 3], dev::nib_byte_to_f128<1>(hi), d1);
-        d0 = fmaf(xs[8 * j + 4], dev::nib_byte_to_f128<2>(lo), d0);
-        d1 = fmaf(xs[8 * j + 5], dev::nib_byte_to_f128<2>(hi), d1);
-        d0 = fmaf(xs[8 * j + 6], dev::nib_byte_to_f128<3>(lo), d0);
-        d1 = fmaf(xs[8 * j + 7], dev::nib_byte_to_f128<3>(hi), d1);
-    }
-    return d0 + d1;
-}
-
-/// The 32 nibbles of `w` as floats 128 + q.
-__device__ __forceinline__ void dequant32_biased(const uint4 &w, float (&qf)[32])
-{
-    const uint32_t words[4] = {w.x, w.y, w.z, w.w};
-#pragma unroll
-    for (int j = 0; j < 4; ++j) {
-        const uint32_t lo = words[j] & 0x0f0f0f0fu;
-        const uint32_t hi = (words[j] >> 4) & 0x0f0f0f0fu;
-        qf[8 * j + 0] = dev::nib_byte_to_f128<0>(lo);
-        qf[8 * j + 1] = dev::nib_byte_to_f128<0>(hi);
-        qf[8 * j + 2] = dev::nib_byte_to_f128<1>(lo);
-        qf[8 * j + 3] = dev::nib_byte_to_f128<1>(hi);
-        qf[8 * j + 4] = dev::nib_byte_to_f128<2>(lo);
-        qf[8 * j + 5] = dev::nib_byte_to_f128<2>(hi);
-        qf[8 * j + 6] = dev::nib_byte_to_f128<3>(lo);
-        qf[8 * j + 7] = dev::nib_byte_to_f128<3>(hi);
-    }
-}
-
-/// M activation rows, NB banks (2 for gate/up), R output rows per block.
-template <int M, int NB, int R>
-__global__ void __launch_bounds__(128) q4_gemv_kernel(const Q4GemvParams p)
-{
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
-    int s = 0;
-    if (p.nseg > 1 && blockIdx.x >= p.seg[1].block_begin) s = 1;
-    if (p.nseg > 2 && blockIdx.x >= p.seg[2].block_begin) s = 2;
-    const Q4Seg sg = p.seg[s];
-    const uint32_t rows = sg.rows, cols = p.cols;
-    const uint32_t row0 = (blockIdx.x - sg.block_begin) * R;
-    const uint32_t gpr = cols >> p.group_shift;
-    const size_t row_bytes = cols >> 1;
-    const uint8_t *packed[2] = {sg.packed0, sg.packed1};
-    const uint32_t *sbp[2] = {sg.sb0, sg.sb1};
-
-    float acc[R][NB][M];
-#pragma unroll
-    for (int r = 0; r < R; ++r)
-#pragma unroll
-        for (int b = 0; b < NB; ++b)
-#pragma unroll
-            for (int m = 0; m < M; ++m) acc[r][b][m] = 0.0f;
-
-    for (uint32_t k0 = warp * kChunk + lane * 32; k0 < cols; k0 += nwarps * kChunk) {
-        // Every row's weights first: R * NB independent 16-byte loads in flight.
-        uint4 wq[R][NB];
-        uint32_t sbw[R][NB];
-        const uint32_t g = k0 >> p.group_shift;
-#pragma unroll
-        for (int r = 0; r < R; ++r) {
-            // Rows past the bank's end re-read its last row; their sums are never stored.
-            const uint32_t row = min(row0 + r, rows - 1);
-#pragma unroll
-            for (int b = 0; b < NB; ++b) {
-                wq[r][b] = dev::ldg_stream16(packed[b] + row * row_bytes + (k0 >> 1));
-                sbw[r][b] = dev::ldg_stream4(sbp[b] + (size_t)row * gpr + g);
-            }
-        }
-        if constexpr (M == 1) {
-            float xs[32];
-            const uint4 *xp = reinterpret_cast<const uint4 *>(p.x + k0);
-#pragma unroll
-            for (int v = 0; v < 4; ++v) {
-                const uint4 xv = __ldg(xp + v);
-                const uint32_t xw[4] = {xv.x, xv.y, xv.z, xv.w};
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    xs[8 * v + 2 * j] = dev::bf16_lo(xw[j]);
-                    xs[8 * v + 2 * j + 1] = dev::bf16_hi(xw[j]);
-                }
-            }
-            float part[8];
-#pragma unroll
-            for (int i = 0; i < 8; ++i) part[i] = (xs[4 * i] + xs[4 * i + 1]) + (xs[4 * i + 2] + xs[4 * i + 3]);
-            const float xsum = ((part[0] + part[1]) + (part[2] + part[3])) + ((part[4] + part[5]) + (part[6] + part[7]));
-#pragma unroll
-            for (int r = 0; r < R; ++r) {
-#pragma unroll
-                for (int b = 0; b < NB; ++b) {
-                    const float dot = fmaf(-128.0f, xsum, dot32_biased(wq[r][b], xs));
-                    const float scale = dev::bf16_lo(sbw[r][b]), bias = dev::bf16_hi(sbw[r][b]);
-                    acc[r][b][0] = fmaf(scale, dot, fmaf(bias, xsum, acc[r][b][0]));
-                }
-            }
-        } else {
-            // Small batch: the weights of a row are expanded once and every
-            // activation row is run against them; x stays packed and is widened
-            // as it is used.
-            uint4 xq[M][4];
-            float xsum[M];
-#pragma unroll
-            for (int m = 0; m < M; ++m) {
-                const uint4 *xp = reinterpret_cast<const uint4 *>(p.x + (size_t)m * cols + k0);
-                float t = 0.0f;
-#pragma unroll
-                for (int v = 0; v < 4; ++v) {
-                    xq[m][v] = __ldg(xp + v);
-                    const uint32_t xw[4] = {xq[m][v].x, xq[m][v].y, xq[m][v].z, xq[m][v].w};
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) t += dev::bf16_lo(xw[j]) + dev::bf16_hi(xw[j]);
-                }
-                xsum[m] = t;
-            }
-#pragma unroll
-            for (int r = 0; r < R; ++r) {
-                float qf[32];
-                dequant32_biased(wq[r][0], qf);
-                const float scale = dev::bf16_lo(sbw[r][0]), bias = dev::bf16_hi(sbw[r][0]);
-#pragma unroll
-                for (int m = 0; m < M; ++m) {
-                    float d0 = 0.0f, d1 = 0.0f;
-#pragma unroll
-                    for (int v = 0; v < 4; ++v) {
-                        const uint32_t xw[4] = {xq[m][v].x, xq[m][v].y, xq[m][v].z, xq[m][v].w};
-#pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            d0 = fmaf(dev::bf16_lo(xw[j]), qf[8 * v + 2 * j], d0);
-                            d1 = fmaf(dev::bf16_hi(xw[j]), qf[8 * v + 2 * j + 1], d1);
-                        }
-                    }
-                    const float dot = fmaf(-128.0f, xsum[m], d0 + d1);
-                    acc[r][0][m] = fmaf(scale, dot, fmaf(bias, xsum[m], acc[r][0][m]));
-                }
-            }
-        }
-    }
-
-    // Lanes, then warps (fixed order), then the epilogue: one thread per output.
-    __shared__ float red[4][R * NB * M];
-#pragma unroll
-    for (int r = 0; r < R; ++r)
-#pragma unroll
-        for (int b = 0; b < NB; ++b)
-#pragma unroll
-            for (int m = 0; m < M; ++m) {
-                const float v = dev::warp_sum(acc[r][b][m]);
-                if (lane == 0) red[warp][(r * NB + b) * M + m] = v;
-            }
-    __syncthreads();
-    const int t = threadIdx.x;
-    if (t < R * M) {
-        const int r = t / M, m = t % M;
-        const uint32_t row = row0 + r;
-        if (row < rows) {
-            float sum[NB];
-#pragma unroll
-            for (int b = 0; b < NB; ++b) {
-                float v = red[0][(r * NB + b) * M + m];
-                for (int w = 1; w < nwarps; ++w) v += red[w][(r * NB + b) * M + m];
-                sum[b] = v;
-            }
-            const size_t idx = (size_t)m * rows + row;
-            float v = sum[0];
-            if (p.epi == EPI_ADD_RESID) {
-                v = v + sg.resid[idx];
-            } else if (p.epi == EPI_GATE_UP_SILU) {
-                v = dev::silu(sum[0]) * sum[NB - 1];
-            } else if (p.epi == EPI_GATE_UP_GELU) {
-                v = dev::gelu_pytorch_tanh(sum[0]) * sum[NB - 1];
-            }
-            if (p.out_bf16) {
-                static_cast<uint16_t *>(sg.out)[idx] = dev::f32_to_bf16_store(v);
-            } else {
-                static_cast<float *>(sg.out)[idx] = v;
-            }
-        }
-    }
-}
+using q4k::EPI_ADD_RESID;
+using q4k::EPI_GATE_UP_GELU;
+using q4k::EPI_GATE_UP_SILU;
+using q4k::EPI_STORE;
+using Q4Seg = q4k::Seg;
+using Q4GemvParams = q4k::Params;
 
 __global__ void swiglu_kernel(const float *gate, const float *up, void *out, uint32_t n, int out_bf16)
 {
@@ -288,58 +62,69 @@ uint32_t log2_u32(uint32_t v)
     return s;
 }
 
-template <int M, int NB, int R>
-Result launch_one(TesslRuntime *rt, const Q4GemvParams &p, uint32_t blocks, int warps)
+template <int M, int NB, int R, int NCH>
+Result launch_one(TesslRuntime *rt, Q4GemvParams &p, int warps)
 {
-    q4_gemv_kernel<M, NB, R><<<blocks, warps * 32, 0, rt->stream>>>(p);
+    auto kernel = q4k::q4_gemv_kernel<M, NB, R, NCH>;
+    uint32_t groups = 0;
+    for (int s = 0; s < p.nseg; ++s) {
+        p.seg[s].group_begin = groups;
+        groups += (p.seg[s].rows + R - 1) / R;
+    }
+    p.ngroups = groups;
+    if (groups == 0) return ok();
+    // Persistent grid: as many blocks as stay resident, each walking its share of the groups.
+    static int per_sm[9] = {0, 0, 0, 0, 0, 0, 0, 0, 0};
+    if (per_sm[warps] == 0) {
+        int n = 0;
+        cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, warps * 32, 0);
+        if (e != cudaSuccess || n < 1) n = 1;
+        per_sm[warps] = n;
+    }
+    const uint32_t grid = std::min<uint32_t>(groups, (uint32_t)(rt->sm_count * per_sm[warps]));
+    kernel<<<grid, warps * 32, 0, rt->stream>>>(p);
     rt->dispatch_count += 1;
     return cuda_check(rt, cudaGetLastError(), "q4_gemv launch");
 }
 
-/// Rows per block: as many as keep the grid at a few blocks per SM.
-int pick_rows_per_block(const TesslRuntime *rt, uint64_t total_rows, int max_r)
-{
-    int r = max_r;
-    while (r > 2 && (total_rows + r - 1) / r < (uint64_t)(3 * rt->sm_count)) r >>= 1;
-    return r;
-}
-
-/// Fills block_begin for each segment and launches the right instantiation.
+/// Picks the split of K over warps (a function of `cols` only, so a row's
+/// summation order never depends on the launch) and the matching instantiation.
 Result launch_q4_gemv(TesslRuntime *rt, Q4GemvParams p, int m, int nb)
 {
-    uint64_t total_rows = 0;
-    for (int s = 0; s < p.nseg; ++s) total_rows += p.seg[s].rows;
-    const int warps = (int)std::min<uint32_t>(4u, (p.cols + kChunk - 1) / kChunk);
-    const int max_r = (m == 1 && nb == 1) ? 16 : (m == 1 ? 8 : (m <= 2 ? 8 : (m <= 4 ? 4 : 2)));
-    const int r = pick_rows_per_block(rt, total_rows, max_r);
-    uint32_t blocks = 0;
-    for (int s = 0; s < p.nseg; ++s) {
-        p.seg[s].block_begin = blocks;
-        blocks += (p.seg[s].rows + r - 1) / r;
+    const uint32_t nchunks = std::max<uint32_t>(1u, (p.cols + q4k::kChunk - 1) / q4k::kChunk);
+    if (m == 1) {
+        int warps, nch;
+        if (nchunks <= 4) {
+            warps = (int)nchunks, nch = 1;
+        } else if (nchunks <= 16) {
+            warps = (int)(nchunks + 1) / 2, nch = 2;
+        } else if (nchunks <= 32) {
+            warps = (int)(nchunks + 3) / 4, nch = 4;
+        } else {
+            warps = 8, nch = 0;
+        }
+        if (nb == 1) {
+            if (nch == 1) return launch_one<1, 1, 8, 1>(rt, p, warps);
+            if (nch == 2) return launch_one<1, 1, 4, 2>(rt, p, warps);
+            if (nch == 4) return launch_one<1, 1, 2, 4>(rt, p, warps);
+            return launch_one<1, 1, 8, 0>(rt, p, warps);
+        }
+        if (nch == 1) return launch_one<1, 2, 4, 1>(rt, p, warps);
+        if (nch == 2) return launch_one<1, 2, 2, 2>(rt, p, warps);
+        if (nch == 4) return launch_one<1, 2, 1, 4>(rt, p, warps);
+        return launch_one<1, 2, 4, 0>(rt, p, warps);
     }
-    if (blocks == 0) return ok();
-#define TESSL_CASE(MM, NBB, RR) \
-    if (m == MM && nb == NBB && r == RR) return launch_one<MM, NBB, RR>(rt, p, blocks, warps)
-    TESSL_CASE(1, 1, 16);
-    TESSL_CASE(1, 1, 8);
-    TESSL_CASE(1, 1, 4);
-    TESSL_CASE(1, 1, 2);
-    TESSL_CASE(1, 2, 8);
-    TESSL_CASE(1, 2, 4);
-    TESSL_CASE(1, 2, 2);
-    TESSL_CASE(2, 1, 8);
-    TESSL_CASE(2, 1, 4);
-    TESSL_CASE(2, 1, 2);
-    TESSL_CASE(3, 1, 4);
-    TESSL_CASE(3, 1, 2);
-    TESSL_CASE(4, 1, 4);
-    TESSL_CASE(4, 1, 2);
-    TESSL_CASE(5, 1, 2);
-    TESSL_CASE(6, 1, 2);
-    TESSL_CASE(7, 1, 2);
-    TESSL_CASE(8, 1, 2);
-#undef TESSL_CASE
-    return fmt("q4_gemv: no kernel for m=%d banks=%d rows_per_block=%d", m, nb, r);
+    const int warps = (int)std::min<uint32_t>(4u, nchunks);
+    switch (m) {
+    case 2: return launch_one<2, 1, 4, 0>(rt, p, warps);
+    case 3: return launch_one<3, 1, 2, 0>(rt, p, warps);
+    case 4: return launch_one<4, 1, 2, 0>(rt, p, warps);
+    case 5: return launch_one<5, 1, 2, 0>(rt, p, warps);
+    case 6: return launch_one<6, 1, 2, 0>(rt, p, warps);
+    case 7: return launch_one<7, 1, 2, 0>(rt, p, warps);
+    case 8: return launch_one<8, 1, 2, 0>(rt, p, warps);
+    default: return fmt("q4_gemv: no kernel for m=%d", m);
+    }
 }
 
 Q4Seg make_seg(const TesslQ4MlxBank &b0, const TesslQ4MlxBank *b1, const TesslBuf &out, const TesslBuf *resid,
