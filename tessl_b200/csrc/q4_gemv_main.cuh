@@ -64,27 +64,45 @@ __global__ void __launch_bounds__(256) q4_gemv_kernel(const Params p)
         }
     }
 
+    // Per-lane constants of the resident form: which of the warp's chunks this
+    // lane has columns in, and the byte / group offsets of its slice.
+    bool live_c[NC];
+    uint32_t koff[NC], goff[NC];
+#pragma unroll
+    for (int c = 0; c < NC; ++c) {
+        const uint32_t k0 = (warp + c * nwarps) * kChunk + lane * 32;
+        live_c[c] = k0 < cols;
+        koff[c] = k0 >> 1;
+        goff[c] = k0 >> p.group_shift;
+    }
+
+    // `full`: all R rows of the group exist (only a bank's last group can be short;
+    // its missing rows re-read the last row and their sums are never stored).
     auto load_unit = [&](Unit<NB, R, NC> &u, const Where &w, uint32_t chunk_base) {
+        const bool full = w.row0 + R <= w.sg.rows;
 #pragma unroll
         for (int c = 0; c < NC; ++c) {
-            const uint32_t k0 = (chunk_base + c * nwarps) * kChunk + lane * 32;
-            const bool live = k0 < cols;
-            const uint32_t g = k0 >> p.group_shift;
+            bool live;
+            uint32_t ko, go;
+            if constexpr (NCH == 0) {
+                const uint32_t k0 = (chunk_base + c * nwarps) * kChunk + lane * 32;
+                live = k0 < cols, ko = k0 >> 1, go = k0 >> p.group_shift;
+            } else {
+                live = live_c[c], ko = koff[c], go = goff[c];
+            }
+            if (!live) continue;  // the buffers were zeroed once; a dead lane never overwrites them
+            const uint8_t *pk0 = w.sg.packed0 + (size_t)w.row0 * row_bytes + ko;
+            const uint32_t *sb0 = w.sg.sb0 + (size_t)w.row0 * gpr + go;
+            const uint8_t *pk1 = NB == 2 ? w.sg.packed1 + (size_t)w.row0 * row_bytes + ko : nullptr;
+            const uint32_t *sb1 = NB == 2 ? w.sg.sb1 + (size_t)w.row0 * gpr + go : nullptr;
 #pragma unroll
             for (int r = 0; r < R; ++r) {
-                // Rows past the bank's end re-read its last row; their sums are never stored.
-                const uint32_t row = min(w.row0 + r, w.sg.rows - 1);
-#pragma unroll
-                for (int b = 0; b < NB; ++b) {
-                    const uint8_t *pk = b == 0 ? w.sg.packed0 : w.sg.packed1;
-                    const uint32_t *sb = b == 0 ? w.sg.sb0 : w.sg.sb1;
-                    if (live) {
-                        u.wq[r][c][b] = dev::ldg_stream16(pk + row * row_bytes + (k0 >> 1));
-                        u.sbw[r][c][b] = dev::ldg_stream4(sb + (size_t)row * gpr + g);
-                    } else {
-                        u.wq[r][c][b] = make_uint4(0, 0, 0, 0);
-                        u.sbw[r][c][b] = 0;
-                    }
+                const uint32_t rr = full ? (uint32_t)r : min((uint32_t)r, w.sg.rows - 1 - w.row0);
+                u.wq[r][c][0] = dev::ldg_stream16(pk0 + rr * row_bytes);
+                u.sbw[r][c][0] = dev::ldg_stream4(sb0 + (size_t)rr * gpr);
+                if constexpr (NB == 2) {
+                    u.wq[r][c][1] = dev::ldg_stream16(pk1 + rr * row_bytes);
+                    u.sbw[r][c][1] = dev::ldg_stream4(sb1 + (size_t)rr * gpr);
                 }
             }
         }
@@ -174,6 +192,15 @@ __global__ void __launch_bounds__(256) q4_gemv_kernel(const Params p)
     uint32_t g = blockIdx.x, step = 0;
     if (g >= p.ngroups) return;
     Unit<NB, R, NC> ua, ub;
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+#pragma unroll
+        for (int c = 0; c < NC; ++c)
+#pragma unroll
+            for (int b = 0; b < NB; ++b) {
+                ua.wq[r][c][b] = ub.wq[r][c][b] = make_uint4(0, 0, 0, 0);
+                ua.sbw[r][c][b] = ub.sbw[r][c][b] = 0;
+            }
     Where wa = locate(p, g, R), wb = wa;
     uint32_t ca = warp, cb = warp;  // chunk base of the unit in each buffer
     bool have_a = true, have_b = false;
