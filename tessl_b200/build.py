@@ -48,6 +48,7 @@ def build(force: bool = False, verbose_ptxas: bool = False) -> Path:
         cmd += ["-ccbin", host_cxx]
     if verbose_ptxas:
         cmd += ["-Xptxas", "-v"]
+    cmd += os.environ.get("TESSL_B200_NVCC_FLAGS", "").split()
     cmd += ["-o", str(LIB)] + [str(CSRC / s) for s in SOURCES]
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:

@@ -7,6 +7,10 @@
 // validation in the reference's order and wording, the choice of instantiation,
 // the launch.
 #include "q4_gemv_main.cuh"
+#include "q4_gemv_warp.cuh"
+#include "q4_gemv_tma.cuh"
+
+#include <cstdlib>
 #include "runtime.h"
 
 namespace tessl {
@@ -87,11 +91,154 @@ Result launch_one(TesslRuntime *rt, Q4GemvParams &p, int warps)
     return cuda_check(rt, cudaGetLastError(), "q4_gemv launch");
 }
 
+template <int NB, int R, int NCH>
+Result launch_warp(TesslRuntime *rt, const Q4GemvParams &p)
+{
+    auto kernel = q4k::q4_gemv_warp_kernel<NB, R, NCH>;
+    static int per_sm = 0;
+    if (per_sm == 0) {
+        int n = 0;
+        cudaError_t e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, 32, 0);
+        per_sm = (e != cudaSuccess || n < 1) ? 1 : n;
+    }
+    q4k::WarpParams wp{};
+    uint64_t total_rows = 0;
+    for (int s = 0; s < p.nseg; ++s) total_rows += p.seg[s].rows;
+    if (total_rows == 0) return ok();
+    // One wave: every warp gets the same number of consecutive rows.
+    const uint64_t capacity = (uint64_t)rt->sm_count * per_sm;
+    uint64_t r = (total_rows + capacity - 1) / capacity;
+    r = (r + R - 1) / R * R;
+    uint32_t blocks = 0;
+    for (int s = 0; s < p.nseg; ++s) {
+        const Q4Seg &a = p.seg[s];
+        wp.seg[s] = q4k::WarpSeg{a.packed0, a.sb0, a.packed1, a.sb1, a.out, a.resid, a.rows, blocks};
+        blocks += (uint32_t)((a.rows + r - 1) / r);
+    }
+    wp.nseg = p.nseg;
+    wp.rows_per_block = (uint32_t)r;
+    wp.x = p.x, wp.cols = p.cols, wp.group_shift = p.group_shift, wp.epi = p.epi, wp.out_bf16 = p.out_bf16;
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(blocks), cfg.blockDim = dim3(32), cfg.dynamicSmemBytes = 0, cfg.stream = rt->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr, cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kernel, wp);
+    rt->dispatch_count += 1;
+    return cuda_check(rt, e, "q4_gemv launch");
+}
+
+/// Experiment knobs for the staged kernel: "consumers,ring_kib,blocks_per_sm".
+struct TmaCfg {
+    int consumers = 16, ring_kib = 148, blocks_per_sm = 1, head_stages = 1, enabled = 1;
+};
+const TmaCfg &tma_cfg()
+{
+    static TmaCfg c = [] {
+        TmaCfg t;
+        if (const char *e = std::getenv("TESSL_B200_GEMV_TMA")) {
+            int a = 0, b = 0, d = 0, h = 0;
+            const int n = std::sscanf(e, "%d,%d,%d,%d", &a, &b, &d, &h);
+            if (n >= 4 && h > 0) t.head_stages = h;
+            if (n >= 1 && a == 0) t.enabled = 0;
+            if (n >= 1 && a > 0) t.consumers = std::min(a, 16);
+            if (n >= 2 && b > 0) t.ring_kib = b;
+            if (n >= 3 && d > 0) t.blocks_per_sm = d;
+        }
+        return t;
+    }();
+    return c;
+}
+
+template <int NB, int RS, int NCH>
+Result launch_tma(TesslRuntime *rt, const Q4GemvParams &p)
+{
+    auto kernel = q4k::q4_gemv_tma_kernel<NB, RS, NCH>;
+    const TmaCfg &cfg = tma_cfg();
+    q4k::TmaParams tp{};
+    uint32_t rb = 0;
+    for (int s = 0; s < p.nseg; ++s) {
+        const Q4Seg &a = p.seg[s];
+        tp.seg[s] = q4k::TmaSeg{a.packed0, a.sb0, a.packed1, a.sb1, a.out, a.resid, a.rows, rb};
+        rb += (a.rows + RS - 1) / RS;
+    }
+    if (rb == 0) return ok();
+    tp.nseg = p.nseg, tp.total_rb = rb;
+    tp.x = p.x, tp.cols = p.cols, tp.group_shift = p.group_shift, tp.epi = p.epi, tp.out_bf16 = p.out_bf16;
+    tp.status = rt->status_dev;
+#ifdef TESSL_GEMV_TIMING
+    tp.timing = nullptr;
+    if (const char *e = std::getenv("TESSL_B200_TIMING_PTR")) tp.timing = (unsigned long long *)std::strtoull(e, nullptr, 0);
+#endif
+    const uint32_t stage_bytes = NB * RS * ((p.cols >> 1) + (p.cols >> p.group_shift) * 4);
+    const uint32_t warps = (uint32_t)cfg.consumers;
+    const uint32_t stages = std::max<uint32_t>(1u, (uint32_t)cfg.ring_kib * 1024u / (stage_bytes * warps));
+    tp.stages = stages;
+    tp.head_stages = (uint32_t)cfg.head_stages;
+    const size_t smem = (size_t)warps * stages * (stage_bytes + 8);
+    static size_t smem_set = 0;
+    if (smem > smem_set) {
+        TESSL_TRY(cuda_check(rt, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
+                             "q4_gemv_tma: shared memory opt-in"));
+        smem_set = smem;
+    }
+    const uint32_t grid = std::min<uint32_t>(rb, (uint32_t)(rt->sm_count * cfg.blocks_per_sm));
+    cudaLaunchConfig_t lc{};
+    lc.gridDim = dim3(grid), lc.blockDim = dim3(cfg.consumers * 32), lc.dynamicSmemBytes = smem;
+    lc.stream = rt->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    lc.attrs = attr, lc.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&lc, kernel, tp);
+    rt->dispatch_count += 1;
+    return cuda_check(rt, e, "q4_gemv launch");
+}
+
+/// The staged kernel needs every bulk copy 16-byte aligned and sized.
+bool tma_ok(const Q4GemvParams &p)
+{
+    if (!tma_cfg().enabled) return false;
+    if (p.cols == 0 || p.cols > 4096) return false;
+    if ((((p.cols >> p.group_shift) * 4) & 15u) != 0) return false;
+    for (int s = 0; s < p.nseg; ++s) {
+        const Q4Seg &a = p.seg[s];
+        if (((uintptr_t)a.sb0 & 15u) || (a.sb1 && ((uintptr_t)a.sb1 & 15u))) return false;
+    }
+    return true;
+}
+
 /// Picks the split of K over warps (a function of `cols` only, so a row's
 /// summation order never depends on the launch) and the matching instantiation.
 Result launch_q4_gemv(TesslRuntime *rt, Q4GemvParams p, int m, int nb)
 {
     const uint32_t nchunks = std::max<uint32_t>(1u, (p.cols + q4k::kChunk - 1) / q4k::kChunk);
+    if (m == 1 && nchunks <= 4 && tma_ok(p)) {
+        if (nb == 1) {
+            if (nchunks == 1) return launch_tma<1, 8, 1>(rt, p);
+            if (nchunks == 2) return launch_tma<1, 4, 2>(rt, p);
+            if (nchunks == 3) return launch_tma<1, 2, 3>(rt, p);
+            return launch_tma<1, 2, 4>(rt, p);
+        }
+        if (nchunks == 1) return launch_tma<2, 4, 1>(rt, p);
+        if (nchunks == 2) return launch_tma<2, 2, 2>(rt, p);
+        if (nchunks == 3) return launch_tma<2, 1, 3>(rt, p);
+        return launch_tma<2, 1, 4>(rt, p);
+    }
+    if (m == 1 && nchunks <= 4) {
+        // Rows of at most 4096 columns: one warp keeps all of x resident.
+        if (nb == 1) {
+            if (nchunks == 1) return launch_warp<1, 8, 1>(rt, p);
+            if (nchunks == 2) return launch_warp<1, 4, 2>(rt, p);
+            if (nchunks == 3) return launch_warp<1, 2, 3>(rt, p);
+            return launch_warp<1, 2, 4>(rt, p);
+        }
+        if (nchunks == 1) return launch_warp<2, 4, 1>(rt, p);
+        if (nchunks == 2) return launch_warp<2, 2, 2>(rt, p);
+        if (nchunks == 3) return launch_warp<2, 1, 3>(rt, p);
+        return launch_warp<2, 1, 4>(rt, p);
+    }
     if (m == 1) {
         int warps, nch;
         if (nchunks <= 4) {
