@@ -1,0 +1,557 @@
+#!/usr/bin/env python
+"""Benchmark of the MLX Q4 decode projection set on B200 (and its CPU reference arm).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+A "step" is one token's pass over one layer's Q4 g64 projections at batch 1,
+hidden 4096: fused q/k/v 4096->6144, o_proj 4096->4096, fused gate/up + SiLU
+4096->2x12288 (bf16 mid), down 12288->4096 - one operator call per projection,
+through the C ABI of libtessl_b200.so. Weights are seeded synthetic banks
+(uniform nibbles, bf16 scale ~U(0.002, 0.02), bias = -8*scale + N(0, 0.001)); the
+step rotates over several layers' banks so the weight stream never fits L2.
+
+Printed: ONE JSON line. `value` is effective weight bandwidth (algorithmic
+weight bytes of the step / device time) with everything resident in HBM;
+`e2e` is the same through synchronous C-ABI calls with the activations copied
+from pinned host memory and the result read back every step; `roofline`
+describes the dominant kernel; `cpu_baseline` times the CPU oracle on the same
+workload. `extra` adds the single-GEMV target shape, the prefill GEMM and the
+other configurations.
+
+With --gpus N > 1 (launched by torchrun, one rank per GPU) the large outputs
+(gate/up, down) are column-sharded over the ranks and all-gathered with NCCL;
+q/k/v and o_proj are small and run replicated. Total work is fixed: "strong".
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+HIDDEN, QKV, INTER, GROUP = 4096, 6144, 12288, 64
+METRIC = "Q4 GEMV effective weight GB/s"
+
+
+def q4_weight_bytes(rows: int, cols: int, group: int = GROUP) -> int:
+    """Algorithmic bytes of a bank: packed nibbles + one bf16 (scale, bias) pair per group."""
+    return rows * cols // 2 + rows * (cols // group) * 4
+
+
+STEP_WEIGHT_BYTES = (q4_weight_bytes(QKV, HIDDEN) + q4_weight_bytes(HIDDEN, HIDDEN)
+                     + 2 * q4_weight_bytes(INTER, HIDDEN) + q4_weight_bytes(HIDDEN, INTER))
+
+
+def load_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]),
+                "bf16_tflops_sustained": float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device: int):
+        self.device, self.rows, self.proc = device, [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-i", str(self.device)], stdout=subprocess.PIPE, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *a):
+        if self.proc:
+            time.sleep(0.15)
+            self.proc.terminate()
+
+    def summary(self):
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            try:
+                sm.append(float(r[1])), mx.append(float(r[2]))
+            except (ValueError, IndexError):
+                continue
+            for n, v in zip(names, r[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        if not sm:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# --------------------------------------------------------------- CPU arm ---
+
+def cpu_step_inputs(seed: int):
+    """One layer's banks and activations as numpy arrays (seeded splitmix64)."""
+    from tessl_b200 import synth
+    shapes = {"qkv": (QKV, HIDDEN), "o": (HIDDEN, HIDDEN), "gate": (INTER, HIDDEN), "up": (INTER, HIDDEN),
+              "down": (HIDDEN, INTER)}
+    banks = {}
+    for i, (name, (r, c)) in enumerate(shapes.items()):
+        p, sb = synth.q4_bank(seed + 16 * i, r, c, GROUP)
+        banks[name] = (p.view(np.uint8).reshape(-1), sb.reshape(-1), r, c)
+    xs = {n: synth.normal_bf16(seed + 1000 + i, HIDDEN) for i, n in enumerate(("x_qkv", "x_o", "x_mlp"))}
+    return banks, xs
+
+
+def cpu_step(banks, xs, threads: int, rows_fraction: float = 1.0):
+    """The decode projection set on the CPU oracle (f64-accumulated dequant-matvec).
+    `rows_fraction` < 1 runs the leading share of each projection's rows (a bounded sample)."""
+    from oracle import api
+    from tessl_b200 import synth
+
+    def mv(name, x):
+        p, sb, r, c = banks[name]
+        rr = max(8, int(r * rows_fraction)) if rows_fraction < 1.0 else r
+        return api.q4_dense_gemm(p[: rr * c // 2], sb[: rr * (c // GROUP) * 2], x, 1, rr, c, GROUP, threads)[0], rr
+
+    done = 0
+    _, rr = mv("qkv", xs["x_qkv"]); done += q4_weight_bytes(rr, HIDDEN)
+    _, rr = mv("o", xs["x_o"]); done += q4_weight_bytes(rr, HIDDEN)
+    g, rr = mv("gate", xs["x_mlp"])
+    u, _ = mv("up", xs["x_mlp"]); done += 2 * q4_weight_bytes(rr, HIDDEN)
+    gd = g.astype(np.float64)
+    mid = (gd / (1.0 + np.exp(-gd)) * u).astype(np.float32)
+    mid_full = np.zeros(INTER, np.float32)
+    mid_full[: mid.size] = mid
+    y, rr = mv("down", synth.f32_to_bf16_bits(mid_full)); done += q4_weight_bytes(rr, INTER)
+    return y, done
+
+
+def run_reference_arm(args, rank: int):
+    """`--impl reference`: the reference's own algorithm for this path on the host
+    cores. The reference is a Metal/Rust crate that cannot be built or run here,
+    so this is the CPU oracle port (oracle/tessl_oracle.c) with every host thread."""
+    if rank != 0:
+        return
+    from oracle import api
+    threads = api.max_threads()
+    banks, xs = cpu_step_inputs(0x7E550100)
+    frac = 0.25  # a bounded sample: the leading quarter of every projection's rows
+    for _ in range(max(1, args.warmup)):
+        cpu_step(banks, xs, threads, frac)
+    t0 = time.perf_counter()
+    done = 0
+    for _ in range(args.steps):
+        _, b = cpu_step(banks, xs, threads, frac)
+        done += b
+    dt = time.perf_counter() - t0
+    gbs = done / dt / 1e9
+    line = {
+        "impl": "reference", "metric": METRIC, "value": gbs, "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "f64 accumulate over bf16 x / Q4 weights", "data": "synthetic",
+        "config": workload_config(args.gpus),
+        "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": threads, "kind": "port",
+                         "sample": f"leading {frac:.0%} of the rows of each projection, {args.steps} steps"},
+        "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(n_gpus: int, layers: int = 4):
+    return {
+        "workload": "qwen3.5-style decode projection set, Q4 g64, M=1, hidden 4096: qkv 4096->6144, o 4096->4096, "
+                    "gate+up+SiLU 4096->2x12288, down 12288->4096",
+        "calls_per_step": 4, "weight_bytes_per_step": STEP_WEIGHT_BYTES,
+        "l2": f"weights rotate over {layers} layers' banks ({layers * STEP_WEIGHT_BYTES / 1e6:.0f} MB > 126 MB L2), "
+              "one layer per step",
+        "parallelism": "single GPU" if n_gpus == 1 else
+        f"gate/up and down column-sharded over {n_gpus} GPUs with NCCL all-gather of bf16 outputs; qkv, o replicated",
+    }
+
+
+# --------------------------------------------------------------- GPU arm ---
+
+class Layer:
+    """One layer's banks on this rank's GPU (sharded where the workload shards)."""
+
+    def __init__(self, torch, nn, sharded, seed: int, world: int, rank: int):
+        self.keep = []
+        gen = torch.Generator(device="cuda")
+        gen.manual_seed(seed)
+
+        def bank(rows, cols):
+            packed = torch.randint(0, 2**31 - 1, (rows, cols // 8), dtype=torch.int32, device="cuda", generator=gen)
+            packed = packed * 2 + torch.randint(0, 2, packed.shape, dtype=torch.int32, device="cuda", generator=gen)
+            sc = (torch.rand((rows, cols // GROUP), device="cuda", generator=gen) * 0.018 + 0.002).to(torch.bfloat16)
+            bi = (-8.0 * sc.float() + 0.001 * torch.randn(sc.shape, device="cuda", generator=gen)).to(torch.bfloat16)
+            return packed, torch.stack([sc, bi], dim=-1).contiguous()
+
+        def take(rows, cols, shard_it):
+            packed, sb = bank(rows, cols)
+            sh = sharded.make_shard(rows, world if shard_it else 1, rank if shard_it else 0)
+            if shard_it and world > 1:
+                packed, sb = sharded.slice_bank(packed, sb, sh)
+            self.keep += [packed, sb]
+            return nn.Q4MlxBank(nn.GpuBuffer.from_torch(packed), nn.GpuBuffer.from_torch(sb)), sh
+
+        self.qkv, _ = take(QKV, HIDDEN, False)
+        self.o, _ = take(HIDDEN, HIDDEN, False)
+        self.gate, self.sh_mid = take(INTER, HIDDEN, True)
+        self.up, _ = take(INTER, HIDDEN, True)
+        self.down, self.sh_out = take(HIDDEN, INTER, True)
+
+
+def run_ours(args, rank: int, world: int, local_rank: int):
+    import torch
+    import torch.distributed as dist
+
+    from tessl_b200 import build as tb
+    from tessl_b200 import nn, sharded
+
+    tb.build()
+    torch.cuda.set_device(local_rank)
+    rt = nn.Runtime(local_rank)
+    st = torch.cuda.ExternalStream(rt.stream, device=local_rank)
+    peaks = load_peaks()
+    n_layers = 4
+    layers = [Layer(torch, nn, sharded, 0x7E550000 + 97 * i, world, rank) for i in range(n_layers)]
+    dev = torch.device("cuda", local_rank)
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(0x7E55)
+    acts = {n: torch.randn(HIDDEN, device=dev, generator=gen).to(torch.bfloat16) for n in ("x_qkv", "x_o", "x_mlp")}
+    qkv_out = torch.empty(QKV, device=dev)
+    o_out = torch.empty(HIDDEN, device=dev)
+    mid_local = torch.empty(layers[0].sh_mid.local_rows, device=dev, dtype=torch.bfloat16)
+    mid_full = torch.empty(INTER, device=dev, dtype=torch.bfloat16) if world > 1 else mid_local
+    y_local = torch.empty(layers[0].sh_out.local_rows, device=dev)
+    B = nn.GpuBuffer.from_torch
+    bufs = {k: B(v) for k, v in acts.items()}
+    qkv_b, o_b, midl_b, midf_b, yl_b = B(qkv_out), B(o_out), B(mid_local), B(mid_full), B(y_local)
+    sq = nn.QuantShape(QKV, HIDDEN, GROUP)
+    so = nn.QuantShape(HIDDEN, HIDDEN, GROUP)
+    sg = nn.QuantShape(layers[0].sh_mid.local_rows, HIDDEN, GROUP)
+    sd = nn.QuantShape(layers[0].sh_out.local_rows, INTER, GROUP)
+    launches_per_step = 4
+
+    def step(i: int):
+        L = layers[i % n_layers]
+        nn.gemv_q4_mlx_simd(rt, L.qkv, bufs["x_qkv"], qkv_b, sq)
+        nn.gemv_q4_mlx_simd(rt, L.o, bufs["x_o"], o_b, so)
+        nn.gemv_q4_mlx_gate_up_silu(rt, L.gate, L.up, bufs["x_mlp"], midl_b, sg, True)
+        if world > 1:
+            with torch.cuda.stream(st):
+                mid = sharded.all_gather_rows(mid_local, L.sh_mid)
+                mid_full.copy_(mid.reshape(-1))
+        nn.gemv_q4_mlx_simd(rt, L.down, midf_b, yl_b, sd)
+        if world > 1:
+            with torch.cuda.stream(st):
+                return sharded.all_gather_rows(y_local, L.sh_out)
+        return y_local
+
+    def barrier():
+        rt.synchronize()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+
+    rt.set_encode_only(True)
+    for i in range(max(args.warmup, 3)):
+        step(i)
+    barrier()
+
+    # Launch-bound inner loop: one CUDA graph holds all K steps (single GPU only;
+    # with NCCL in the step the calls are enqueued directly).
+    graph = None
+    if world == 1:
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=st):
+            for i in range(args.steps):
+                step(i)
+        with torch.cuda.stream(st):
+            graph.replay()
+        barrier()
+
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(local_rank) as clocks:
+        barrier()
+        with torch.cuda.stream(st):
+            e0.record(st)
+            if graph is not None:
+                graph.replay()
+            else:
+                for i in range(args.steps):
+                    step(i)
+            e1.record(st)
+        barrier()
+    ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    ms_per_step = ms / args.steps
+    value = STEP_WEIGHT_BYTES / (ms_per_step * 1e-3) / 1e9
+
+    # ---- per-projection device times (one graph per projection, same rotation) ----
+    per_kernel = {}
+    if world == 1:
+        def time_graph(fn, iters):
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=st):
+                for i in range(iters):
+                    fn(i)
+            best = 1e30
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            with torch.cuda.stream(st):
+                for rep in range(6):
+                    a.record(st)
+                    g.replay()
+                    b.record(st)
+                    b.synchronize()
+                    if rep:
+                        best = min(best, a.elapsed_time(b) / iters)
+            return best * 1e3  # us per launch
+
+        iters = max(16, min(args.steps, 200))
+        gate_f32 = torch.empty(INTER, device=dev)
+        gate_f32_b = B(gate_f32)
+        shapes = {
+            "qkv 6144x4096": (lambda i: nn.gemv_q4_mlx_simd(rt, layers[i % n_layers].qkv, bufs["x_qkv"], qkv_b, sq),
+                              q4_weight_bytes(QKV, HIDDEN)),
+            "o 4096x4096": (lambda i: nn.gemv_q4_mlx_simd(rt, layers[i % n_layers].o, bufs["x_o"], o_b, so),
+                            q4_weight_bytes(HIDDEN, HIDDEN)),
+            "gate_up_silu 2x12288x4096": (lambda i: nn.gemv_q4_mlx_gate_up_silu(
+                rt, layers[i % n_layers].gate, layers[i % n_layers].up, bufs["x_mlp"], midl_b, sg, True),
+                2 * q4_weight_bytes(INTER, HIDDEN)),
+            "down 4096x12288": (lambda i: nn.gemv_q4_mlx_simd(rt, layers[i % n_layers].down, midf_b, yl_b, sd),
+                                q4_weight_bytes(HIDDEN, INTER)),
+            "gemv 12288x4096 (target shape)": (lambda i: nn.gemv_q4_mlx_simd(
+                rt, layers[i % n_layers].gate, bufs["x_mlp"], gate_f32_b, nn.QuantShape(INTER, HIDDEN, GROUP)),
+                q4_weight_bytes(INTER, HIDDEN)),
+        }
+        for name, (fn, nbytes) in shapes.items():
+            us = time_graph(fn, iters)
+            per_kernel[name] = {"us": round(us, 3), "weight_gbs": round(nbytes / us / 1e3, 1),
+                                "frac_of_measured_hbm": round(nbytes / us / 1e3 / peaks["hbm_gbs"], 4)}
+    rt.set_encode_only(False)
+    return dict(torch=torch, dist=dist, nn=nn, rt=rt, st=st, layers=layers, acts=acts, step=step, ms_per_step=ms_per_step,
+                value=value, clocks=clocks.summary(), per_kernel=per_kernel, peaks=peaks, dev=dev,
+                launches_per_step=launches_per_step, n_layers=n_layers, y_local=y_local, bufs=bufs)
+
+
+def measure_e2e(ctx, args):
+    """The same step through synchronous C-ABI calls (every call returns idle, as the
+    reference's C ABI does), activations copied from pinned host memory each step
+    and the down-projection output read back to the host each step."""
+    torch, nn, rt = ctx["torch"], ctx["nn"], ctx["rt"]
+    host_x = {k: v.cpu().pin_memory() for k, v in ctx["acts"].items()}
+    y = ctx["y_local"]
+    host_y = np.empty(y.numel(), np.float32)
+    yb = nn.GpuBuffer(y.data_ptr(), y.numel() * 4, owner=y, rt=rt)
+    xin = {k: nn.GpuBuffer(v.data_ptr(), v.numel() * 2, owner=v, rt=rt) for k, v in ctx["acts"].items()}
+    h2d = sum(v.numel() * 2 for v in host_x.values())
+    d2h = host_y.nbytes
+    steps = max(10, min(args.steps, 100))
+
+    def one(i):
+        for k, v in host_x.items():
+            xin[k].write(v.numpy().view(np.uint16))
+        ctx["step"](i)
+        host_y[:] = yb.read(np.float32, host_y.size)
+
+    for i in range(3):
+        one(i)
+    rt.synchronize()
+    t0 = time.perf_counter()
+    for i in range(steps):
+        one(i)
+    rt.synchronize()
+    dt = (time.perf_counter() - t0) / steps
+    return {"value": STEP_WEIGHT_BYTES / dt / 1e9, "unit": "GB/s", "h2d_bytes_per_step": h2d,
+            "d2h_bytes_per_step": d2h, "ms_per_step": dt * 1e3, "steps": steps,
+            "how": "4 synchronous C-ABI operator calls + 3 host->device writes + 1 device->host read per step"}
+
+
+def measure_extra(ctx, args):
+    """Other configurations of the path, each timed on the device with CUDA events
+    (single GPU): LM head, small-batch GEMM, MLX Q8 GEMV, and the Q4 prefill GEMM."""
+    torch, nn, rt, st, dev, peaks = ctx["torch"], ctx["nn"], ctx["rt"], ctx["st"], ctx["dev"], ctx["peaks"]
+    B = nn.GpuBuffer.from_torch
+    out = {}
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(0xC0FFEE)
+
+    def rand_bank(rows, cols):
+        packed = torch.randint(0, 2**31 - 1, (rows, cols // 8), dtype=torch.int32, device=dev, generator=gen)
+        sc = (torch.rand((rows, cols // GROUP), device=dev, generator=gen) * 0.018 + 0.002).to(torch.bfloat16)
+        bi = (-8.0 * sc.float() + 0.001 * torch.randn(sc.shape, device=dev, generator=gen)).to(torch.bfloat16)
+        sb = torch.stack([sc, bi], dim=-1).contiguous()
+        return (packed, sb), nn.Q4MlxBank(B(packed), B(sb))
+
+    def timed(fn, nrot, iters):
+        rt.set_encode_only(True)
+        for i in range(nrot):
+            fn(i)
+        rt.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=st):
+            for i in range(iters):
+                fn(i % nrot)
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        best = 1e30
+        with torch.cuda.stream(st):
+            for rep in range(5):
+                a.record(st)
+                g.replay()
+                b.record(st)
+                b.synchronize()
+                if rep:
+                    best = min(best, a.elapsed_time(b) / iters)
+        rt.set_encode_only(False)
+        return best * 1e3
+
+    # LM head 151936 x 4096, M = 1 and 8 (two banks = 700 MB > L2)
+    vocab = 151936
+    keep, lm = zip(*[rand_bank(vocab, HIDDEN) for _ in range(2)])
+    wb = q4_weight_bytes(vocab, HIDDEN)
+    for m in (1, 8):
+        x = torch.randn(m * HIDDEN, device=dev, generator=gen).to(torch.bfloat16)
+        y = torch.empty(m * vocab, device=dev)
+        shape = nn.QuantShape(vocab, HIDDEN, GROUP)
+        if m == 1:
+            us = timed(lambda i: nn.gemv_q4_mlx_simd(rt, lm[i], B(x), B(y), shape), 2, 8)
+        else:
+            us = timed(lambda i: nn.gemm_q4_mlx(rt, lm[i], B(x), B(y), shape, m), 2, 4)
+        out[f"lm_head 151936x4096 m={m}"] = {"us": round(us, 2), "weight_gbs": round(wb / us / 1e3, 1),
+                                            "frac_of_measured_hbm": round(wb / us / 1e3 / peaks["hbm_gbs"], 4)}
+    del keep, lm
+    torch.cuda.empty_cache()
+
+    # MLX Q8 GEMV 14336 x 4096, M in {1, 4, 8} (six banks = 374 MB > L2)
+    n8 = 14336
+    codes = [torch.randint(0, 2**31 - 1, (n8, HIDDEN // 4), dtype=torch.int32, device=dev, generator=gen) for _ in range(6)]
+    sc = (torch.rand((n8, HIDDEN // GROUP), device=dev, generator=gen) * 0.0045 + 0.0005).to(torch.bfloat16)
+    sb8 = torch.stack([sc, (-128.0 * sc.float()).to(torch.bfloat16)], dim=-1).contiguous()
+    wb8 = n8 * HIDDEN + n8 * (HIDDEN // GROUP) * 4
+    for m in (1, 4, 8):
+        x = torch.randn(m * HIDDEN, device=dev, generator=gen).to(torch.bfloat16)
+        y = torch.empty(m * n8, device=dev)
+        us = timed(lambda i: nn.gemm_q8_mlx(rt, B(codes[i]), B(sb8), B(x), B(y), nn.QuantShape(n8, HIDDEN, GROUP), m),
+                   6, 24)
+        out[f"q8_mlx 14336x4096 m={m}"] = {"us": round(us, 2), "weight_gbs": round(wb8 / us / 1e3, 1),
+                                          "frac_of_measured_hbm": round(wb8 / us / 1e3 / peaks["hbm_gbs"], 4)}
+    del codes
+    torch.cuda.empty_cache()
+
+    # Q4 prefill GEMM: X [2048, 4096] x W [12288, 4096]^T, f32 out
+    M, N, K = 2048, INTER, HIDDEN
+    try:
+        keep, banks = zip(*[rand_bank(N, K) for _ in range(2)])
+        X = torch.randn(M * K, device=dev, generator=gen).to(torch.bfloat16)
+        Y = torch.empty(M * N, device=dev)
+        us = timed(lambda i: nn.gemm_q4_mlx_tensorops(rt, banks[i], B(X), B(Y), nn.QuantShape(N, K, GROUP), M), 2, 6)
+        tf = 2.0 * M * N * K / us / 1e6
+        out["prefill_gemm 2048x12288x4096"] = {"us": round(us, 1), "tflops": round(tf, 1),
+                                                "frac_of_measured_bf16_burst": round(tf / peaks["bf16_tflops"], 4),
+                                                "frac_of_measured_bf16_sustained": round(tf / peaks["bf16_tflops_sustained"], 4)}
+    except nn.TesslError as e:
+        out["prefill_gemm 2048x12288x4096"] = {"error": str(e)}
+    return out
+
+
+def cpu_baseline(args):
+    """The CPU oracle on one full step of the same workload, all host threads."""
+    from oracle import api
+    threads = api.max_threads()
+    banks, xs = cpu_step_inputs(0x7E550100)
+    cpu_step(banks, xs, threads, 0.1)
+    t0 = time.perf_counter()
+    _, done = cpu_step(banks, xs, threads, 1.0)
+    dt = time.perf_counter() - t0
+    return {"value": done / dt / 1e9, "unit": "GB/s", "cores": threads, "kind": "port",
+            "sample": "one full step (all rows of the four projections), f64-accumulated dequant-matvec in C/OpenMP",
+            "seconds": round(dt, 3)}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-extra", action="store_true", help="skip the other configurations (faster)")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        if args.steps > 40:
+            args.steps = 40  # each step is ~0.1-0.5 s of CPU work; keep the arm to a few minutes
+        run_reference_arm(args, rank)
+        return
+    if world > 1:
+        import torch.distributed as dist
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        import torch
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    ctx = run_ours(args, rank, world, local_rank)
+    peaks = ctx["peaks"]
+    line = {
+        "metric": METRIC, "value": round(ctx["value"], 1), "unit": "GB/s", "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": round(ctx["ms_per_step"], 5), "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f32 accumulate over bf16 x / Q4 weights", "data": "synthetic",
+        "config": workload_config(world, ctx["n_layers"]),
+        "gpu_launches": ctx["launches_per_step"] * args.steps,
+        "clocks": ctx["clocks"],
+        "frac_of_measured_hbm": round(ctx["value"] / (peaks["hbm_gbs"] * world), 4),
+        "frac_of_nominal_8tbs": round(ctx["value"] / (8000.0 * world), 4),
+    }
+    if world == 1:
+        pk = ctx["per_kernel"]
+        # Dominant kernel: the bulk-copy staged GEMV (qkv, o and gate/up launches of a step).
+        dom = ["qkv 6144x4096", "o 4096x4096", "gate_up_silu 2x12288x4096"]
+        dom_bytes = q4_weight_bytes(QKV, HIDDEN) + q4_weight_bytes(HIDDEN, HIDDEN) + 2 * q4_weight_bytes(INTER, HIDDEN)
+        dom_us = sum(pk[k]["us"] for k in dom)
+        achieved = dom_bytes / dom_us / 1e3
+        line["roofline"] = {
+            "bound": "hbm", "kernel": "q4_gemv_tma_kernel", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"],
+            "unit": "GB/s", "frac": round(achieved / peaks["hbm_gbs"], 4), "peak_source": peaks["source"],
+            # ncu: dram__bytes_read+write of one 12288x4096 launch was 28.35 MB for 28.31 MB algorithmic
+            # (profiles/q4_gemv_12288x4096.md): traffic = algorithmic bytes x 1.0015 per launch.
+            "traffic": round(dom_bytes / 3 * 1.0015), "algorithmic_bytes_per_launch": dom_bytes // 3,
+            "launches_per_step": 3,
+        }
+        line["per_kernel"] = pk
+        line["e2e"] = measure_e2e(ctx, args)
+        if not args.no_extra:
+            line["extra"] = measure_extra(ctx, args)
+        line["cpu_baseline"] = cpu_baseline(args)
+    else:
+        line["e2e"] = None
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        ctx["dist"].barrier()
+        ctx["dist"].destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,98 @@
+"""Column sharding of an MLX Q4 bank over the GPUs of one node.
+
+Output rows are independent (every output row of `W x` reads only its own
+packed row and scale/bias pairs), so a bank is cut into contiguous row slices,
+one per rank; each GPU streams only its slice from its own HBM, and one
+all-gather of the bf16 (or f32) outputs over NVLink rebuilds the full vector.
+The activation vector (a few KiB) is replicated. The reference is a
+single-device library; this module has no counterpart there.
+
+The partition and the gather are plain `torch.distributed` code and work on any
+backend (NCCL on GPUs, gloo on CPU for the tests); the local product is done by
+whatever `compute` callable the caller supplies, which on a GPU is the
+`tessl_b200.nn` operator on the rank's slice.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Callable, List, Tuple
+
+import torch
+import torch.distributed as dist
+
+
+def shard_rows(rows: int, world: int, rank: int, align: int = 8) -> Tuple[int, int]:
+    """Rows [begin, end) of rank `rank`: contiguous, `align`-row aligned slices
+    of ceil(rows / world) rounded up to `align`; trailing ranks may get fewer
+    rows or none."""
+    if world <= 0 or not (0 <= rank < world):
+        raise ValueError(f"rank {rank} outside world {world}")
+    per = -(-rows // world)
+    per = -(-per // align) * align
+    begin = min(rows, rank * per)
+    return begin, min(rows, begin + per)
+
+
+def slice_rows_per_rank(rows: int, world: int, align: int = 8) -> int:
+    """The padded slice height every rank contributes to the all-gather."""
+    per = -(-rows // world)
+    return -(-per // align) * align
+
+
+@dataclass
+class RowShard:
+    """This rank's slice of a [rows, ...] row-major array."""
+    rows: int
+    world: int
+    rank: int
+    begin: int
+    end: int
+
+    @property
+    def local_rows(self) -> int:
+        return self.end - self.begin
+
+
+def make_shard(rows: int, world: int, rank: int, align: int = 8) -> RowShard:
+    b, e = shard_rows(rows, world, rank, align)
+    return RowShard(rows, world, rank, b, e)
+
+
+def slice_bank(packed: torch.Tensor, scales_biases: torch.Tensor, shard: RowShard):
+    """The rank's rows of a bank given as [rows, cols/8] words and [rows, groups, 2] pairs."""
+    return packed[shard.begin:shard.end].contiguous(), scales_biases[shard.begin:shard.end].contiguous()
+
+
+def all_gather_rows(local: torch.Tensor, shard: RowShard, m: int = 1, group=None, align: int = 8) -> torch.Tensor:
+    """All-gather of per-rank outputs `local` [m, local_rows] into [m, rows].
+
+    Every rank contributes a slice padded to the common height, the gather is
+    one `all_gather_into_tensor`, and the padding is dropped afterwards. With
+    m == 1 and rows divisible by world * align no copy is needed beyond the
+    collective itself."""
+    per = slice_rows_per_rank(shard.rows, shard.world, align)
+    local = local.reshape(m, shard.local_rows)
+    if shard.local_rows != per:
+        padded = local.new_zeros((m, per))
+        padded[:, : shard.local_rows] = local
+        local = padded
+    gathered = local.new_empty((shard.world, m, per))
+    dist.all_gather_into_tensor(gathered, local.contiguous(), group=group)
+    # [world, m, per] -> [m, world * per] -> first `rows` columns
+    return gathered.permute(1, 0, 2).reshape(m, shard.world * per)[:, : shard.rows].contiguous()
+
+
+def sharded_matvec(compute: Callable[[RowShard], torch.Tensor], rows: int, m: int = 1, group=None,
+                   align: int = 8) -> torch.Tensor:
+    """Runs `compute(shard)` (this rank's [m, local_rows] outputs) and gathers [m, rows]."""
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    rank = dist.get_rank(group) if dist.is_initialized() else 0
+    shard = make_shard(rows, world, rank, align)
+    local = compute(shard)
+    if world == 1:
+        return local.reshape(m, rows)
+    return all_gather_rows(local, shard, m, group, align)
+
+
+def partition_table(rows: int, world: int, align: int = 8) -> List[Tuple[int, int]]:
+    return [shard_rows(rows, world, r, align) for r in range(world)]
