@@ -1,6 +1,612 @@
-// placeholder replaced by the tcgen05 kernel
+// MLX Q4 prefill GEMM on the tcgen05 tensor cores:
+//
+//     Y[M, N] = X[M, K] (bf16) . W[N, K]^T,   W = scale * q + bias per group of G along K
+//
+// the replacement for the reference's `nn::gemm_q4_mlx_tensorops`
+// (src/nn.rs:4683-4757; kernels/gemm_q4_mlx_tensorops.metal in the reference
+// project). The reference keeps the integer nibbles exact in its matrix unit and
+// folds the affine in f32; rounding the dequantized weight to bf16 (8 significand
+// bits) would not stay inside the stated output tolerance, so this kernel keeps
+// the products exact too, with f16 operands:
+//
+//     W = s * (q - 8) + (b + 8 s)
+//
+//   * s * (q - 8) has at most 8 + 3 significand bits: exact in f16 (for
+//     2^-17 <= |s| <= 8188; real MLX scales are 1e-4 .. 1e-1). It is the B operand,
+//     produced in shared memory from the packed nibbles.
+//   * X is converted bf16 -> f16 once per call by a small pre-pass, after an exact
+//     per-row power-of-two rescale so any finite bf16 row fits f16's range; the
+//     scale is undone in the epilogue. That is the A operand.
+//   * The remaining rank-K/G term sum_g xsum[m, g] * (b + 8 s)[n, g] rides along
+//     as extra K columns: the pre-pass appends, per group, the f32 group sum of x
+//     split into three f16 pieces (h1, h2, h3, h1) and the dequant warps emit
+//     (c1, c1, c1, c2) with c1 + c2 the two-piece f16 split of b + 8 s. Four
+//     extra columns per group, ~6% more MMA work at G = 64.
+//
+// Every product is exact and accumulation is f32 in TMEM, so the result obeys
+// the reference's own bound gamma_t * S (tests/gemm_q4_mlx_tensorops.rs:11-21 of
+// the reference project).
+//
+// Structure (one CTA per SM, persistent over 128 x BN output tiles):
+//   warp 0      TMA producer: X tile (128 x 64 f16, 128B swizzle) and packed W
+//               tile (BN rows x 32 bytes) per 64-wide K block, plain
+//               cp.async.bulk.tensor loads (no multicast).
+//   warp 1      allocates TMEM (512 columns = two BN-wide f32 accumulators) and
+//               issues tcgen05.mma (cta_group::1, kind::f16, M = 128, N = BN,
+//               K = 16, four per K block), committing to mbarriers.
+//   warps 2-5   epilogue: tcgen05.ld of the finished accumulator, row scale,
+//               stores; overlaps the next tile's main loop.
+//   warps 6..   BN/32 dequant warps, one thread per weight row: 32 packed bytes
+//               from shared memory -> 64 f16 values s * (q - 8) written in the
+//               128B-swizzled K-major layout the MMA descriptor expects.
+// All mbarrier waits are bounded (see q4_gemv_tma.cuh); on a timeout the status
+// word is set, every role leaves its loops and TMEM is released.
+#include <cuda.h>
+#include <cuda_fp16.h>
+
+#include <algorithm>
+
+#include "q4_gemv_tma.cuh"
 #include "runtime.h"
-namespace tessl { namespace nn {
+
+namespace tessl {
+namespace {
+
+using q4k::and_or;
+using q4k::lds128;
+using q4k::mbar_arrive;
+using q4k::mbar_expect_tx;
+using q4k::mbar_init;
+using q4k::mbar_try;
+using q4k::mbar_wait;
+using q4k::smem_u32;
+
+constexpr int BM = 128;  // rows of X per tile = MMA M
+constexpr int BK = 64;   // K block: 128 bytes of f16 = one swizzle row
+constexpr uint32_t kTmemCols = 512;
+
+struct GemmParams {
+    const uint32_t *sb;   // bf16 (scale, bias) pairs [N, K / G]
+    const float *row_scale;  // [M] power-of-two scale removed from each X row
+    void *y;
+    uint32_t M, N, K;
+    uint32_t gshift;       // log2 G
+    uint32_t gpr;          // K / G
+    uint32_t nkb_main;     // ceil(K / 64)
+    uint32_t nkb_extra;    // ceil(4 * gpr / 64)
+    uint32_t tiles_m, tiles_n;
+    int out_bf16;
+    uint32_t *status;
+};
+
+// ---------------------------------------------------------------- PTX wrappers ---
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int x, int y, uint32_t bar)
+{
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+            dst),
+        "l"(map), "r"(x), "r"(y), "r"(bar)
+        : "memory");
+}
+__device__ __forceinline__ void tcgen05_commit(uint32_t bar)
+{
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tcgen05_fence_after()
+{
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tcgen05_fence_before()
+{
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+/// D[tmem] (+)= A[smem] . B[smem]^T for one K = 16 slice.
+__device__ __forceinline__ void tcgen05_mma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                                uint32_t accumulate)
+{
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+/// Shared-memory matrix descriptor: K-major tile, 128-byte swizzle, rows 128 B
+/// apart, 8-row groups 1024 B apart, descriptor version 1 (sm_100).
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr)
+{
+    return (uint64_t)((smem_addr & 0x3ffffu) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) |
+           ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32])
+{
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,"
+        "%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+}
+__device__ __forceinline__ uint32_t h2_sub(uint32_t a, uint32_t b)
+{
+    uint32_t r;
+    asm("sub.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+    return r;
+}
+__device__ __forceinline__ uint32_t h2_mul(uint32_t a, uint32_t b)
+{
+    uint32_t r;
+    asm("mul.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+    return r;
+}
+__device__ __forceinline__ uint32_t h2_fma(uint32_t a, uint32_t b, uint32_t c)
+{
+    uint32_t r;
+    asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(c));
+    return r;
+}
+__device__ __forceinline__ uint32_t pack_h2(__half lo, __half hi)
+{
+    return (uint32_t)__half_as_ushort(lo) | ((uint32_t)__half_as_ushort(hi) << 16);
+}
+
+// ------------------------------------------------------- activation pre-pass ---
+
+/// One block per X row: finds the row's exponent, writes the row as f16 scaled by
+/// an exact power of two into the augmented A matrix (K padded to 64, elements of
+/// every 8-chunk in the order 0,4,1,5,2,6,3,7 that the nibble-pair dequant
+/// produces on the B side), then the per-group sums as (h1, h2, h3, h1) f16
+/// quadruples, then zero padding. a_aug is [M, K_aug] row-major.
+__global__ void __launch_bounds__(256) x_prepare_kernel(const uint16_t *x, __half *a_aug, float *row_scale, uint32_t K,
+                                                        uint32_t K64, uint32_t K_aug, uint32_t gshift)
+{
+    const uint32_t m = blockIdx.x, tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const uint16_t *xrow = x + (size_t)m * K;
+    __half *arow = a_aug + (size_t)m * K_aug;
+    __shared__ uint32_t red[8];
+    __shared__ float s_down;
+
+    // pass 1: largest magnitude (bf16 bit patterns order like integers); Inf/NaN disable the rescale
+    uint32_t amax = 0;
+    for (uint32_t ch = tid; ch < K / 8; ch += 256) {
+        const uint4 v = __ldg(reinterpret_cast<const uint4 *>(xrow) + ch);
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) amax = max(amax, max(w[j] & 0x7fffu, (w[j] >> 16) & 0x7fffu));
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) amax = max(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    if (lane == 0) red[warp] = amax;
+    __syncthreads();
+    if (tid == 0) {
+        uint32_t a = 0;
+        for (int i = 0; i < 8; ++i) a = max(a, red[i]);
+        int sh = 0;
+        if (a != 0 && a < 0x7f80u) {
+            const int e = (int)(a >> 7) - 127;  // floor(log2 max|x|)
+            // Bring the row maximum to [2^14 / G, 2^15 / G): every element and every
+            // group sum (at most G times the maximum) then fits f16.
+            sh = min(max(e - 14 + (int)gshift, -126), 126);
+        }
+        s_down = __int_as_float((127 - sh) << 23);
+        row_scale[m] = __int_as_float((127 + sh) << 23);
+    }
+    __syncthreads();
+    const float down = s_down;
+
+    // pass 2: convert, permute, group sums
+    const uint32_t gsize8 = (1u << gshift) / 8;  // 8-element chunks per group: 4, 8 or 16
+    const uint32_t gpr = K >> gshift;
+    for (uint32_t base = 0; base < K64 / 8; base += 256) {
+        const uint32_t ch = base + tid;
+        float f[8];
+        if (ch * 8 < K) {
+            const uint4 v = __ldg(reinterpret_cast<const uint4 *>(xrow) + ch);
+            const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                f[2 * j] = __uint_as_float(w[j] << 16) * down;
+                f[2 * j + 1] = __uint_as_float(w[j] & 0xffff0000u) * down;
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) f[j] = 0.0f;
+        }
+        __half h[8];
+        float sum = 0.0f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            h[j] = __float2half_rn(f[j]);
+            sum += __half2float(h[j]);  // the group sum is over the values the MMA will see
+        }
+        if (ch < K64 / 8) {
+            uint4 o;
+            o.x = pack_h2(h[0], h[4]), o.y = pack_h2(h[1], h[5]), o.z = pack_h2(h[2], h[6]), o.w = pack_h2(h[3], h[7]);
+            reinterpret_cast<uint4 *>(arow)[ch] = o;
+        }
+        for (uint32_t o = gsize8 / 2; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+        const uint32_t g = ch / gsize8;
+        if ((ch % gsize8) == 0 && g < gpr) {
+            const __half h1 = __float2half_rn(sum);
+            const float r1 = sum - __half2float(h1);
+            const __half h2 = __float2half_rn(r1);
+            const __half h3 = __float2half_rn(r1 - __half2float(h2));
+            uint2 q;
+            q.x = pack_h2(h1, h2), q.y = pack_h2(h3, h1);
+            *reinterpret_cast<uint2 *>(arow + K64 + 4 * g) = q;
+        }
+    }
+    // pass 3: zero the unused tail of the extra columns
+    for (uint32_t i = 4 * gpr + tid; i < K_aug - K64; i += 256) arow[K64 + i] = __float2half_rn(0.0f);
+}
+
+// ------------------------------------------------------------------ the GEMM ---
+
+template <int BN>
+struct Cfg {
+    static constexpr int SA = 4;                      // X-tile stages
+    static constexpr int SQ = 4;                      // packed-W stages
+    static constexpr int SB = BN == 256 ? 3 : 4;      // dequantized-W stages
+    static constexpr int NDW = BN / 32;               // dequant warps
+    static constexpr int THREADS = (6 + NDW) * 32;
+    static constexpr uint32_t A_BYTES = BM * BK * 2;  // 16 KiB
+    static constexpr uint32_t Q_BYTES = BN * 32;
+    static constexpr uint32_t B_BYTES = BN * BK * 2;
+    static constexpr uint32_t OFF_A = 0;
+    static constexpr uint32_t OFF_B = OFF_A + SA * A_BYTES;
+    static constexpr uint32_t OFF_Q = OFF_B + SB * B_BYTES;
+    static constexpr uint32_t OFF_BAR = OFF_Q + SQ * Q_BYTES;
+    static constexpr int NBARS = 2 * SA + 2 * SQ + 2 * SB + 4 + 1;
+    static constexpr uint32_t SMEM = OFF_BAR + NBARS * 8 + 1024;  // + slack to align the base to 1 KiB
+};
+
+template <int BN>
+__global__ void __launch_bounds__(Cfg<BN>::THREADS, 1)
+    q4_prefill_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+                           const GemmParams p)
+{
+    using C = Cfg<BN>;
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ int abort_flag;
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t bar0 = base + C::OFF_BAR;
+    auto a_full = [&](int s) { return bar0 + 8 * s; };
+    auto a_empty = [&](int s) { return bar0 + 8 * (C::SA + s); };
+    auto q_full = [&](int s) { return bar0 + 8 * (2 * C::SA + s); };
+    auto q_empty = [&](int s) { return bar0 + 8 * (2 * C::SA + C::SQ + s); };
+    auto b_full = [&](int s) { return bar0 + 8 * (2 * C::SA + 2 * C::SQ + s); };
+    auto b_empty = [&](int s) { return bar0 + 8 * (2 * C::SA + 2 * C::SQ + C::SB + s); };
+    auto acc_full = [&](int b) { return bar0 + 8 * (2 * C::SA + 2 * C::SQ + 2 * C::SB + b); };
+    auto acc_empty = [&](int b) { return bar0 + 8 * (2 * C::SA + 2 * C::SQ + 2 * C::SB + 2 + b); };
+    const uint32_t done_bar = bar0 + 8 * (C::NBARS - 1);
+
+    const uint32_t nkb = p.nkb_main + p.nkb_extra;
+    const uint32_t ntiles = p.tiles_m * p.tiles_n;
+
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        for (int s = 0; s < C::SA; ++s) mbar_init(a_full(s), 1), mbar_init(a_empty(s), 1);
+        for (int s = 0; s < C::SQ; ++s) mbar_init(q_full(s), 1), mbar_init(q_empty(s), C::NDW);
+        for (int s = 0; s < C::SB; ++s) mbar_init(b_full(s), C::NDW), mbar_init(b_empty(s), 1);
+        for (int b = 0; b < 2; ++b) mbar_init(acc_full(b), 1), mbar_init(acc_empty(b), 4);
+        mbar_init(done_bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&map_w) : "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)),
+                     "r"(kTmemCols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem_base = tmem_base_slot;
+    volatile int *abortp = &abort_flag;
+    auto fail = [&](uint32_t role, uint32_t where) {
+        *abortp = 1;
+        *(volatile uint32_t *)p.status = (role << 24) | (where & 0xffffffu);
+    };
+
+    if (warp == 0) {
+        // ------------------------------------------------ TMA producer ---
+        if (lane == 0) {
+            uint32_t ia = 0, iq = 0;  // running stage counters
+            bool ok_ = true;
+            for (uint32_t t = blockIdx.x; t < ntiles && ok_; t += gridDim.x) {
+                const int m0 = (int)(t % p.tiles_m) * BM, n0 = (int)(t / p.tiles_m) * BN;
+                for (uint32_t kb = 0; kb < nkb; ++kb) {
+                    const uint32_t sa = ia % C::SA;
+                    if (!mbar_wait(a_empty(sa), ((ia / C::SA) & 1u) ^ 1u, abortp)) {
+                        fail(1, kb);
+                        ok_ = false;
+                        break;
+                    }
+                    mbar_expect_tx(a_full(sa), C::A_BYTES);
+                    tma_load_2d(base + C::OFF_A + sa * C::A_BYTES, &map_a, (int)(kb * BK), m0, a_full(sa));
+                    ++ia;
+                    if (kb < p.nkb_main) {
+                        const uint32_t sq = iq % C::SQ;
+                        if (!mbar_wait(q_empty(sq), ((iq / C::SQ) & 1u) ^ 1u, abortp)) {
+                            fail(2, kb);
+                            ok_ = false;
+                            break;
+                        }
+                        mbar_expect_tx(q_full(sq), C::Q_BYTES);
+                        tma_load_2d(base + C::OFF_Q + sq * C::Q_BYTES, &map_w, (int)(kb * 32), n0, q_full(sq));
+                        ++iq;
+                    }
+                }
+            }
+            // Let every copy this thread issued land before the CTA may exit.
+            for (uint32_t i = ia > (uint32_t)C::SA ? ia - C::SA : 0; i < ia; ++i) {
+                const long long t0 = clock64();
+                while (!mbar_try(a_full(i % C::SA), (i / C::SA) & 1u))
+                    if (clock64() - t0 > 4000000000ll) break;
+            }
+            for (uint32_t i = iq > (uint32_t)C::SQ ? iq - C::SQ : 0; i < iq; ++i) {
+                const long long t0 = clock64();
+                while (!mbar_try(q_full(i % C::SQ), (i / C::SQ) & 1u))
+                    if (clock64() - t0 > 4000000000ll) break;
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------ MMA issuer ---
+        if (lane == 0) {
+            constexpr uint32_t idesc = (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+            uint32_t ia = 0, ib = 0, it = 0;
+            bool ok_ = true;
+            for (uint32_t t = blockIdx.x; t < ntiles && ok_; t += gridDim.x, ++it) {
+                const uint32_t buf = it & 1u;
+                if (!mbar_wait(acc_empty(buf), ((it >> 1) & 1u) ^ 1u, abortp)) {
+                    fail(3, it);
+                    break;
+                }
+                tcgen05_fence_after();
+                const uint32_t d = tmem_base + buf * 256u;
+                for (uint32_t kb = 0; kb < nkb; ++kb) {
+                    const uint32_t sa = ia % C::SA, sb = ib % C::SB;
+                    if (!mbar_wait(a_full(sa), (ia / C::SA) & 1u, abortp) ||
+                        !mbar_wait(b_full(sb), (ib / C::SB) & 1u, abortp)) {
+                        fail(4, kb);
+                        ok_ = false;
+                        break;
+                    }
+                    tcgen05_fence_after();
+                    const uint64_t ad = umma_desc(base + C::OFF_A + sa * C::A_BYTES);
+                    const uint64_t bd = umma_desc(base + C::OFF_B + sb * C::B_BYTES);
+#pragma unroll
+                    for (uint32_t k4 = 0; k4 < 4; ++k4)
+                        tcgen05_mma_f16(d, ad + 2 * k4, bd + 2 * k4, idesc, (kb | k4) != 0 ? 1u : 0u);
+                    tcgen05_commit(a_empty(sa));  // both stages are free once these MMAs have read them
+                    tcgen05_commit(b_empty(sb));
+                    ++ia, ++ib;
+                }
+                if (ok_) tcgen05_commit(acc_full(buf));
+            }
+            // Nothing may still be writing TMEM when it is released below.
+            tcgen05_commit(done_bar);
+            const long long t0 = clock64();
+            while (!mbar_try(done_bar, 0u))
+                if (clock64() - t0 > 4000000000ll) break;
+        }
+    } else if (warp < 6) {
+        // ------------------------------------------------ epilogue ---
+        const uint32_t quarter = (uint32_t)warp & 3u;  // the TMEM lanes this warp may read
+        uint32_t it = 0;
+        for (uint32_t t = blockIdx.x; t < ntiles; t += gridDim.x, ++it) {
+            const uint32_t buf = it & 1u;
+            if (!mbar_wait(acc_full(buf), (it >> 1) & 1u, abortp)) {
+                if (lane == 0) fail(5, it);
+                break;
+            }
+            tcgen05_fence_after();
+            const uint32_t m = (t % p.tiles_m) * BM + quarter * 32 + lane;
+            const uint32_t n0 = (t / p.tiles_m) * BN;
+            const float rs = m < p.M ? p.row_scale[m] : 0.0f;
+            const bool vec4 = (p.N & 3u) == 0, vec8 = (p.N & 7u) == 0;
+#pragma unroll 1
+            for (uint32_t c = 0; c < BN / 32; ++c) {
+                uint32_t r[32];
+                tmem_ld32(tmem_base + ((quarter * 32u) << 16) + buf * 256u + c * 32u, r);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                const uint32_t n = n0 + c * 32;
+                if (m < p.M && n < p.N) {
+                    if (p.out_bf16) {
+                        uint16_t *dst = static_cast<uint16_t *>(p.y) + (size_t)m * p.N + n;
+                        if (vec8 && n + 32 <= p.N) {
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                uint4 o;
+                                uint32_t *ow = &o.x;
+#pragma unroll
+                                for (int k = 0; k < 4; ++k)
+                                    ow[k] = (uint32_t)dev::f32_to_bf16_store(__uint_as_float(r[8 * j + 2 * k]) * rs) |
+                                            ((uint32_t)dev::f32_to_bf16_store(__uint_as_float(r[8 * j + 2 * k + 1]) * rs) << 16);
+                                reinterpret_cast<uint4 *>(dst)[j] = o;
+                            }
+                        } else {
+                            for (uint32_t j = 0; j < 32 && n + j < p.N; ++j)
+                                dst[j] = dev::f32_to_bf16_store(__uint_as_float(r[j]) * rs);
+                        }
+                    } else {
+                        float *dst = static_cast<float *>(p.y) + (size_t)m * p.N + n;
+                        if (vec4 && n + 32 <= p.N) {
+#pragma unroll
+                            for (int j = 0; j < 8; ++j)
+                                reinterpret_cast<float4 *>(dst)[j] =
+                                    make_float4(__uint_as_float(r[4 * j]) * rs, __uint_as_float(r[4 * j + 1]) * rs,
+                                                __uint_as_float(r[4 * j + 2]) * rs, __uint_as_float(r[4 * j + 3]) * rs);
+                        } else {
+                            for (uint32_t j = 0; j < 32 && n + j < p.N; ++j) dst[j] = __uint_as_float(r[j]) * rs;
+                        }
+                    }
+                }
+            }
+            tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(acc_empty(buf));
+        }
+    } else {
+        // ------------------------------------------------ dequant warps ---
+        const uint32_t r = (uint32_t)(warp - 6) * 32 + lane;  // weight row within the tile
+        const uint32_t swz = (r & 7u) << 4;
+        uint32_t iq = 0, ib = 0;
+        bool ok_ = true;
+        for (uint32_t t = blockIdx.x; t < ntiles && ok_; t += gridDim.x) {
+            const uint32_t n = min((t / p.tiles_m) * BN + r, p.N - 1);  // rows past N repeat the last row
+            const uint32_t *sbrow = p.sb + (size_t)n * p.gpr;
+            for (uint32_t kb = 0; kb < nkb; ++kb) {
+                const uint32_t sb = ib % C::SB;
+                if (!mbar_wait(b_empty(sb), ((ib / C::SB) & 1u) ^ 1u, abortp)) {
+                    if (lane == 0) fail(6, kb);
+                    ok_ = false;
+                    break;
+                }
+                const uint32_t brow = base + C::OFF_B + sb * C::B_BYTES + r * 128;
+                if (kb < p.nkb_main) {
+                    const uint32_t sq = iq % C::SQ;
+                    if (!mbar_wait(q_full(sq), (iq / C::SQ) & 1u, abortp)) {
+                        if (lane == 0) fail(7, kb);
+                        ok_ = false;
+                        break;
+                    }
+                    const uint32_t qrow = base + C::OFF_Q + sq * C::Q_BYTES + r * 32;
+                    const uint4 w0 = lds128(qrow), w1 = lds128(qrow + 16);
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(q_empty(sq));  // the packed stage may be refilled
+                    ++iq;
+                    const uint32_t words[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+                    for (int h = 0; h < 2; ++h) {
+                        const uint32_t g = min((kb * 64 + h * 32) >> p.gshift, p.gpr - 1);
+                        const float sc = dev::bf16_lo(__ldg(sbrow + g));
+                        const __half sh = __float2half_rn(sc);
+                        const uint32_t s2 = pack_h2(sh, sh);
+#pragma unroll
+                        for (int c4 = 0; c4 < 4; ++c4) {
+                            const uint32_t w = words[4 * h + c4], w8 = w >> 8;
+                            // (1024 + q) and (1024 + 16 q) as f16 pairs, then q - 8 exactly, then * s exactly
+                            const uint32_t t0 = and_or(w, 0x000f000fu, 0x64006400u);
+                            const uint32_t t1 = and_or(w, 0x00f000f0u, 0x64006400u);
+                            const uint32_t t2 = and_or(w8, 0x000f000fu, 0x64006400u);
+                            const uint32_t t3 = and_or(w8, 0x00f000f0u, 0x64006400u);
+                            uint4 o;
+                            o.x = h2_mul(h2_sub(t0, 0x64086408u), s2);                // 1024 + q - 1032
+                            o.y = h2_mul(h2_fma(t1, 0x2c002c00u, 0xd480d480u), s2);  // (1024 + 16 q) / 16 - 72
+                            o.z = h2_mul(h2_sub(t2, 0x64086408u), s2);
+                            o.w = h2_mul(h2_fma(t3, 0x2c002c00u, 0xd480d480u), s2);
+                            const uint32_t c = 4 * h + c4;
+                            asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(brow + ((c << 4) ^ swz)), "r"(o.x),
+                                         "r"(o.y), "r"(o.z), "r"(o.w)
+                                         : "memory");
+                        }
+                    }
+                } else {
+                    // extra K block: (c1, c1, c1, c2) per group, c1 + c2 = b + 8 s in two f16 pieces
+                    const uint32_t e = kb - p.nkb_main;
+#pragma unroll
+                    for (int c = 0; c < 8; ++c) {
+                        uint32_t o[4];
+#pragma unroll
+                        for (int j = 0; j < 2; ++j) {
+                            const uint32_t g = e * 16 + 2 * c + j;
+                            uint32_t lo = 0, hi = 0;
+                            if (g < p.gpr) {
+                                const uint32_t pair = __ldg(sbrow + g);
+                                const float bp = fmaf(8.0f, dev::bf16_lo(pair), dev::bf16_hi(pair));
+                                const __half c1 = __float2half_rn(bp);
+                                const __half c2 = __float2half_rn(bp - __half2float(c1));
+                                lo = pack_h2(c1, c1), hi = pack_h2(c1, c2);
+                            }
+                            o[2 * j] = lo, o[2 * j + 1] = hi;
+                        }
+                        asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(brow + (((uint32_t)c << 4) ^ swz)),
+                                     "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3])
+                                     : "memory");
+                    }
+                }
+                // generic-proxy stores -> visible to the tensor core's async-proxy reads
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) mbar_arrive(b_full(sb));
+                ++ib;
+            }
+        }
+    }
+
+    tcgen05_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tcgen05_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+    }
+}
+
+// ---------------------------------------------------------------------- host ---
+
+using EncodeTiled = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                 const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                                 CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+Result tensormap_encoder(TesslRuntime *rt, EncodeTiled *out)
+{
+    if (!rt->tensormap_encode) {
+        void *fn = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q);
+        if (e != cudaSuccess || q != cudaDriverEntryPointSuccess || !fn) {
+            cudaGetLastError();
+            return "gemm_q4_mlx_tensorops: the driver does not export cuTensorMapEncodeTiled";
+        }
+        rt->tensormap_encode = fn;
+    }
+    *out = reinterpret_cast<EncodeTiled>(rt->tensormap_encode);
+    return ok();
+}
+
+Result make_map_2d(EncodeTiled enc, CUtensorMap *map, CUtensorMapDataType dt, void *ptr, uint64_t inner, uint64_t outer,
+                   uint64_t row_stride_bytes, uint32_t box_inner, uint32_t box_outer, CUtensorMapSwizzle swz)
+{
+    const cuuint64_t dims[2] = {inner, outer};
+    const cuuint64_t strides[1] = {row_stride_bytes};
+    const cuuint32_t box[2] = {box_inner, box_outer};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = enc(map, dt, 2, ptr, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swz,
+                           CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fmt("gemm_q4_mlx_tensorops: cuTensorMapEncodeTiled failed (%d)", (int)r);
+    return ok();
+}
+
+template <int BN>
+Result launch_gemm(TesslRuntime *rt, const CUtensorMap &ma, const CUtensorMap &mw, GemmParams p)
+{
+    using C = Cfg<BN>;
+    auto kernel = q4_prefill_gemm_kernel<BN>;
+    static bool opted = false;
+    if (!opted) {
+        TESSL_TRY(cuda_check(rt, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM),
+                             "gemm_q4_mlx_tensorops: shared memory opt-in"));
+        opted = true;
+    }
+    p.tiles_n = (p.N + BN - 1) / BN;
+    const uint32_t tiles = p.tiles_m * p.tiles_n;
+    const uint32_t grid = std::min<uint32_t>(tiles, (uint32_t)rt->sm_count);
+    kernel<<<grid, C::THREADS, C::SMEM, rt->stream>>>(ma, mw, p);
+    rt->dispatch_count += 1;
+    return cuda_check(rt, cudaGetLastError(), "gemm_q4_mlx_tensorops launch");
+}
+
+}  // namespace
+
+namespace nn {
+
 uint32_t gemm_q4_mlx_tensorops_max_k(uint32_t m, uint32_t n, uint32_t group_size)
 {
     const uint64_t widest = std::max<uint64_t>(std::max(m, n), 1);
@@ -8,9 +614,89 @@ uint32_t gemm_q4_mlx_tensorops_max_k(uint32_t m, uint32_t n, uint32_t group_size
     const uint64_t g = std::max<uint32_t>(group_size, 1);
     return (uint32_t)(k / g * g);
 }
-Result gemm_q4_mlx_tensorops(TesslRuntime *, const TesslQ4MlxBank &, const TesslBuf &, const TesslBuf &,
-                             const TesslQuantShape &, uint32_t, OutKind)
+
+Result gemm_q4_mlx_tensorops(TesslRuntime *rt, const TesslQ4MlxBank &bank, const TesslBuf &x_bf16, const TesslBuf &y,
+                             const TesslQuantShape &shape, uint32_t m, OutKind out)
 {
-    return "gemm_q4_mlx_tensorops: not built yet";
+    const char *what = "gemm_q4_mlx_tensorops";
+    TESSL_TRY(quant_shape_validate(shape, what));
+    if (shape.group_size != 32 && shape.group_size != 64 && shape.group_size != 128) {
+        return fmt("%s: group_size %u is not one of [32, 64, 128]; the matmul2d descriptor's K is the group, so each "
+                   "size is its own entry point",
+                   what, shape.group_size);
+    }
+    if (shape.cols == 0) return fmt("%s: cols must be non-zero", what);
+    const uint32_t n = shape.rows, k = shape.cols, groups = k / shape.group_size;
+    // The reference kernel's int32 extents; checked before any buffer length so an
+    // oversize shape is named as such (src/nn.rs:4712-4727 of the reference project).
+    TESSL_TRY(require_i32_extent(elems(m, k), "gemm_q4_mlx_tensorops x (m * cols)"));
+    TESSL_TRY(require_i32_extent(elems(n, k), "gemm_q4_mlx_tensorops weights (rows * cols 4-bit elements)"));
+    TESSL_TRY(require_i32_extent(elems(m, n), "gemm_q4_mlx_tensorops y (m * rows)"));
+    TESSL_TRY(require_i32_extent(elems(n, groups), "gemm_q4_mlx_tensorops scale/bias pairs (rows * groups)"));
+    TESSL_TRY(q4_bank_validate(bank, shape, what));
+    TESSL_TRY(require(x_bf16, elems(m, k), 2, std::string(what) + " x_bf16"));
+    TESSL_TRY(require(y, elems(m, n), out == OUT_BF16 ? 2 : 4, std::string(what) + " y"));
+    const Named writes[] = {{"y", &y}};
+    const Named reads[] = {{"packed", &bank.packed}, {"scales_biases", &bank.scales_biases}, {"x_bf16", &x_bf16}};
+    TESSL_TRY(require_disjoint_writes(what, writes, 1, reads, 3));
+    if (m == 0 || n == 0) return ok();
+    TESSL_TRY(require_aligned16(bank.packed, std::string(what) + " packed"));
+    TESSL_TRY(require_aligned16(x_bf16, std::string(what) + " x_bf16"));
+    TESSL_TRY(require_aligned16(y, std::string(what) + " y"));
+    if (((uintptr_t)bank.scales_biases.ptr & 3u) != 0)
+        return fmt("%s scales_biases: device pointer must be 4-byte aligned", what);
+
+    uint32_t gshift = 0;
+    while ((1u << gshift) < shape.group_size) ++gshift;
+    const uint32_t nkb_main = (k + BK - 1) / BK;
+    const uint32_t nkb_extra = (4 * groups + BK - 1) / BK;
+    const uint32_t k64 = nkb_main * BK, k_aug = (nkb_main + nkb_extra) * BK;
+
+    // Scratch: the augmented f16 activations [m, k_aug] and the row scales [m].
+    const size_t a_bytes = ((size_t)m * k_aug * 2 + 255) & ~(size_t)255;
+    void *scratch = nullptr;
+    TESSL_TRY(scratch_reserve(rt, a_bytes + (size_t)m * 4, &scratch));
+    __half *a_aug = static_cast<__half *>(scratch);
+    float *row_scale = reinterpret_cast<float *>(static_cast<char *>(scratch) + a_bytes);
+
+    x_prepare_kernel<<<m, 256, 0, rt->stream>>>(static_cast<const uint16_t *>(x_bf16.ptr), a_aug, row_scale, k, k64,
+                                                k_aug, gshift);
+    rt->dispatch_count += 1;
+    TESSL_TRY(cuda_check(rt, cudaGetLastError(), "gemm_q4_mlx_tensorops pre-pass launch"));
+
+    // Tile width: fewest (waves x width), i.e. least time lost in a partial last wave.
+    const uint32_t tiles_m = (m + BM - 1) / BM;
+    int best_bn = 256;
+    uint64_t best_cost = ~0ull;
+    for (int bn : {256, 192, 128}) {
+        const uint64_t tiles = (uint64_t)tiles_m * ((n + bn - 1) / bn);
+        const uint64_t waves = (tiles + rt->sm_count - 1) / rt->sm_count;
+        const uint64_t cost = waves * (uint64_t)bn;
+        if (cost < best_cost) best_cost = cost, best_bn = bn;
+    }
+
+    EncodeTiled enc = nullptr;
+    TESSL_TRY(tensormap_encoder(rt, &enc));
+    CUtensorMap ma, mw;
+    TESSL_TRY(make_map_2d(enc, &ma, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, a_aug, k_aug, m, (uint64_t)k_aug * 2, BK, BM,
+                          CU_TENSOR_MAP_SWIZZLE_128B));
+    TESSL_TRY(make_map_2d(enc, &mw, CU_TENSOR_MAP_DATA_TYPE_UINT8, bank.packed.ptr, k / 2, n, k / 2, 32,
+                          (uint32_t)best_bn, CU_TENSOR_MAP_SWIZZLE_NONE));
+
+    GemmParams p{};
+    p.sb = static_cast<const uint32_t *>(bank.scales_biases.ptr);
+    p.row_scale = row_scale;
+    p.y = y.ptr;
+    p.M = m, p.N = n, p.K = k;
+    p.gshift = gshift, p.gpr = groups;
+    p.nkb_main = nkb_main, p.nkb_extra = nkb_extra;
+    p.tiles_m = tiles_m;
+    p.out_bf16 = out == OUT_BF16;
+    p.status = rt->status_dev;
+    if (best_bn == 256) return launch_gemm<256>(rt, ma, mw, p);
+    if (best_bn == 192) return launch_gemm<192>(rt, ma, mw, p);
+    return launch_gemm<128>(rt, ma, mw, p);
 }
-}}
+
+}  // namespace nn
+}  // namespace tessl
