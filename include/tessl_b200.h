@@ -211,6 +211,25 @@ TESSL_API int32_t tessl_gemm_q4_mlx_tensorops(TesslRuntime *rt, TesslQ4MlxBank b
 TESSL_API int32_t tessl_gemm_q4_mlx_tensorops_bf16(TesslRuntime *rt, TesslQ4MlxBank bank, TesslBuf x_bf16, TesslBuf y_bf16,
                                          TesslQuantShape shape, uint32_t m, char *err, size_t err_len);
 
+/* tessl_gemm_q4_mlx_tensorops for callers that cannot allocate device memory.
+ * It has no counterpart in the reference. The regular entry keeps its
+ * intermediate data (an f16 copy of X with per-group sums, and one scale per
+ * row) in a buffer it grows with cudaMalloc; a serving loop that forbids
+ * allocation in steady state, code living under another framework's allocator,
+ * or a thread that is capturing its stream cannot afford that call. This entry
+ * uses a fixed 8 MiB array inside the library instead (held by every GPU that
+ * loads the library until the process exits) and refuses, with a message that
+ * names the sizes, any call whose m * K_aug * 2 + m * 4 bytes do not fit
+ * (K_aug = 64 * (ceil(K/64) + ceil(4*(K/G)/64)); e.g. up to m = 963 at K = 4096,
+ * G = 64). Arguments, validation, kernels and results are those of
+ * tessl_gemm_q4_mlx_tensorops. The first call on a device looks the array's
+ * address up; make that call before capturing a stream. All calls on a device
+ * share the array: it keeps the previous call's contents (every byte a call
+ * reads is rewritten by that call first, so nothing needs clearing), and calls
+ * that overlap on the GPU race on it - serialise them. */
+TESSL_API int32_t tessl_gemm_q4_mlx_tensorops_noalloc(TesslRuntime *rt, TesslQ4MlxBank bank, TesslBuf x_bf16, TesslBuf y,
+                                            TesslQuantShape shape, uint32_t m, char *err, size_t err_len);
+
 /* `Q4Weight::matmul` (src/qwen35_q4.rs:518-561): the M-dispatch policy over one
  * bank of group size 64. m == 0 is a no-op, 1 the GEMV, 2..=8 the small-batch
  * kernel, more the tensor-core GEMM (which refuses a residual). x is bf16

@@ -78,6 +78,7 @@ SIGNATURES = {
     "tessl_gemm_q4_mlx_tensorops_max_k": (_u32, [_u32, _u32, _u32]),
     "tessl_gemm_q4_mlx_tensorops": (C.c_int32, [_RT, Q4MlxBank, Buf, Buf, QuantShape, _u32] + _ERR),
     "tessl_gemm_q4_mlx_tensorops_bf16": (C.c_int32, [_RT, Q4MlxBank, Buf, Buf, QuantShape, _u32] + _ERR),
+    "tessl_gemm_q4_mlx_tensorops_noalloc": (C.c_int32, [_RT, Q4MlxBank, Buf, Buf, QuantShape, _u32] + _ERR),
     "tessl_q4_weight_matmul": (C.c_int32, [_RT, Q4MlxBank, _u32, _u32, Buf, _u32, Buf, C.POINTER(Buf)] + _ERR),
     "tessl_q4_weight_gate_up_silu": (C.c_int32, [_RT, Q4MlxBank, Q4MlxBank, _u32, _u32, Buf, Buf, _u32] + _ERR),
     "tessl_gemv_q8": (C.c_int32, [_RT, Buf, Buf, Buf, Buf, Buf, _u32, _u32, _u32] + _ERR),

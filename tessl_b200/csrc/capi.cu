@@ -411,6 +411,14 @@ int32_t tessl_gemm_q4_mlx_tensorops_bf16(TesslRuntime *rt, TesslQ4MlxBank bank, 
     });
 }
 
+int32_t tessl_gemm_q4_mlx_tensorops_noalloc(TesslRuntime *rt, TesslQ4MlxBank bank, TesslBuf x_bf16, TesslBuf y,
+                                            TesslQuantShape shape, uint32_t m, char *err, size_t err_len)
+{
+    return guarded(rt, err, err_len, true, [&] {
+        return tessl::nn::gemm_q4_mlx_tensorops_noalloc(rt, bank, x_bf16, y, shape, m, tessl::nn::OUT_F32);
+    });
+}
+
 int32_t tessl_q4_weight_matmul(TesslRuntime *rt, TesslQ4MlxBank bank, uint32_t rows, uint32_t cols, TesslBuf x_bf16,
                                uint32_t m, TesslBuf y, const TesslBuf *resid, char *err, size_t err_len)
 {

@@ -699,4 +699,144 @@ Result gemm_q4_mlx_tensorops(TesslRuntime *rt, const TesslQ4MlxBank &bank, const
 }
 
 }  // namespace nn
+
+// ------------------------------------------- prefill GEMM without allocation ---
+
+namespace {
+
+/// Upper bound of the built-in scratch: enough for m * K_aug f16 activations plus
+/// m row scales, e.g. 512 rows at K = 4096, G = 64, or 2048 rows at K = 1024.
+constexpr size_t kStaticScratchBytes = size_t(8) << 20;
+
+/// The scratch itself lives in the library image: every GPU that loads the
+/// library holds these 8 MiB until the process exits. In host code this name is
+/// only a stand-in; the device address comes from cudaGetSymbolAddress below.
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+constexpr int kMaxDevices = 64;
+void *g_static_scratch_addr[kMaxDevices] = {};
+
+/// Device address of the built-in scratch on the runtime's device (which the
+/// caller has made current). Looked up once per device, on the first call.
+Result static_scratch_address(TesslRuntime *rt, void **out)
+{
+    if (rt->device < 0 || rt->device >= kMaxDevices)
+        return fmt("gemm_q4_mlx_tensorops_noalloc: device ordinal %d is outside 0..%d", rt->device, kMaxDevices - 1);
+    if (!g_static_scratch_addr[rt->device]) {
+        void *ptr = nullptr;
+        const cudaError_t e = cudaGetSymbolAddress(&ptr, g_static_scratch);
+        if (e != cudaSuccess || !ptr) {
+            cudaGetLastError();
+            return fmt("gemm_q4_mlx_tensorops_noalloc: cannot resolve the built-in scratch on device %d (%s)",
+                       rt->device, cudaGetErrorString(e));
+        }
+        g_static_scratch_addr[rt->device] = ptr;
+    }
+    *out = g_static_scratch_addr[rt->device];
+    return ok();
+}
+
+}  // namespace
+
+namespace nn {
+
+/// `gemm_q4_mlx_tensorops` for callers that must not allocate device memory
+/// while they run: serving loops that forbid anything that can synchronise the
+/// device or fail for lack of memory in steady state, code inside another
+/// framework's allocator discipline, or a thread that is capturing a stream
+/// (where cudaMalloc is an error). The regular entry grows a scratch buffer
+/// with cudaMalloc whenever a call needs more than any earlier one; this one
+/// puts the same intermediate data (the f16 copy of X with its group sums, and
+/// the row scales) into a fixed array inside the library and refuses shapes
+/// that do not fit. Same validation, same kernels, same bits.
+///
+/// The first call on a device resolves the array's address (no allocation, but
+/// a runtime call: make it before any stream capture). The array is shared by
+/// every call and every runtime on that device and keeps the last call's
+/// contents; the pre-pass rewrites every byte a call later reads, so nothing has
+/// to start at zero, but two calls that overlap on the GPU (two streams, two
+/// runtimes) race on it and must be serialised by the caller.
+Result gemm_q4_mlx_tensorops_noalloc(TesslRuntime *rt, const TesslQ4MlxBank &bank, const TesslBuf &x_bf16,
+                                     const TesslBuf &y, const TesslQuantShape &shape, uint32_t m, OutKind out)
+{
+    const char *what = "gemm_q4_mlx_tensorops";
+    TESSL_TRY(quant_shape_validate(shape, what));
+    if (shape.group_size != 32 && shape.group_size != 64 && shape.group_size != 128) {
+        return fmt("%s: group_size %u is not one of [32, 64, 128]; the matmul2d descriptor's K is the group, so each "
+                   "size is its own entry point",
+                   what, shape.group_size);
+    }
+    if (shape.cols == 0) return fmt("%s: cols must be non-zero", what);
+    const uint32_t n = shape.rows, k = shape.cols, groups = k / shape.group_size;
+    TESSL_TRY(require_i32_extent(elems(m, k), "gemm_q4_mlx_tensorops x (m * cols)"));
+    TESSL_TRY(require_i32_extent(elems(n, k), "gemm_q4_mlx_tensorops weights (rows * cols 4-bit elements)"));
+    TESSL_TRY(require_i32_extent(elems(m, n), "gemm_q4_mlx_tensorops y (m * rows)"));
+    TESSL_TRY(require_i32_extent(elems(n, groups), "gemm_q4_mlx_tensorops scale/bias pairs (rows * groups)"));
+    TESSL_TRY(q4_bank_validate(bank, shape, what));
+    TESSL_TRY(require(x_bf16, elems(m, k), 2, std::string(what) + " x_bf16"));
+    TESSL_TRY(require(y, elems(m, n), out == OUT_BF16 ? 2 : 4, std::string(what) + " y"));
+    const Named writes[] = {{"y", &y}};
+    const Named reads[] = {{"packed", &bank.packed}, {"scales_biases", &bank.scales_biases}, {"x_bf16", &x_bf16}};
+    TESSL_TRY(require_disjoint_writes(what, writes, 1, reads, 3));
+    if (m == 0 || n == 0) return ok();
+    TESSL_TRY(require_aligned16(bank.packed, std::string(what) + " packed"));
+    TESSL_TRY(require_aligned16(x_bf16, std::string(what) + " x_bf16"));
+    TESSL_TRY(require_aligned16(y, std::string(what) + " y"));
+    if (((uintptr_t)bank.scales_biases.ptr & 3u) != 0)
+        return fmt("%s scales_biases: device pointer must be 4-byte aligned", what);
+
+    uint32_t gshift = 0;
+    while ((1u << gshift) < shape.group_size) ++gshift;
+    const uint32_t nkb_main = (k + BK - 1) / BK;
+    const uint32_t nkb_extra = (4 * groups + BK - 1) / BK;
+    const uint32_t k64 = nkb_main * BK, k_aug = (nkb_main + nkb_extra) * BK;
+    const size_t a_bytes = ((size_t)m * k_aug * 2 + 255) & ~(size_t)255;
+    const size_t need = a_bytes + (size_t)m * 4;
+    if (need > kStaticScratchBytes) {
+        return fmt("gemm_q4_mlx_tensorops_noalloc: m = %u rows of %u columns need %zu bytes of scratch but the "
+                   "built-in scratch holds %zu; use gemm_q4_mlx_tensorops, which allocates",
+                   m, k, need, kStaticScratchBytes);
+    }
+    void *scratch = nullptr;
+    TESSL_TRY(static_scratch_address(rt, &scratch));
+    __half *a_aug = static_cast<__half *>(scratch);
+    float *row_scale = reinterpret_cast<float *>(static_cast<char *>(scratch) + a_bytes);
+
+    x_prepare_kernel<<<m, 256, 0, rt->stream>>>(static_cast<const uint16_t *>(x_bf16.ptr), a_aug, row_scale, k, k64,
+                                                k_aug, gshift);
+    rt->dispatch_count += 1;
+    TESSL_TRY(cuda_check(rt, cudaGetLastError(), "gemm_q4_mlx_tensorops pre-pass launch"));
+
+    const uint32_t tiles_m = (m + BM - 1) / BM;
+    int best_bn = 256;
+    uint64_t best_cost = ~0ull;
+    for (int bn : {256, 192, 128}) {
+        const uint64_t tiles = (uint64_t)tiles_m * ((n + bn - 1) / bn);
+        const uint64_t waves = (tiles + rt->sm_count - 1) / rt->sm_count;
+        const uint64_t cost = waves * (uint64_t)bn;
+        if (cost < best_cost) best_cost = cost, best_bn = bn;
+    }
+    EncodeTiled enc = nullptr;
+    TESSL_TRY(tensormap_encoder(rt, &enc));
+    CUtensorMap ma, mw;
+    TESSL_TRY(make_map_2d(enc, &ma, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, a_aug, k_aug, m, (uint64_t)k_aug * 2, BK, BM,
+                          CU_TENSOR_MAP_SWIZZLE_128B));
+    TESSL_TRY(make_map_2d(enc, &mw, CU_TENSOR_MAP_DATA_TYPE_UINT8, bank.packed.ptr, k / 2, n, k / 2, 32,
+                          (uint32_t)best_bn, CU_TENSOR_MAP_SWIZZLE_NONE));
+    GemmParams p{};
+    p.sb = static_cast<const uint32_t *>(bank.scales_biases.ptr);
+    p.row_scale = row_scale;
+    p.y = y.ptr;
+    p.M = m, p.N = n, p.K = k;
+    p.gshift = gshift, p.gpr = groups;
+    p.nkb_main = nkb_main, p.nkb_extra = nkb_extra;
+    p.tiles_m = tiles_m;
+    p.out_bf16 = out == OUT_BF16;
+    p.status = rt->status_dev;
+    if (best_bn == 256) return launch_gemm<256>(rt, ma, mw, p);
+    if (best_bn == 192) return launch_gemm<192>(rt, ma, mw, p);
+    return launch_gemm<128>(rt, ma, mw, p);
+}
+
+}  // namespace nn
 }  // namespace tessl

@@ -237,6 +237,14 @@ def gemm_q4_mlx_tensorops(rt: Runtime, bank: Q4MlxBank, x_bf16: GpuBuffer, y: Gp
     capi.call(name, rt.handle, bank.c(), x_bf16.c(), y.c(), shape.c(), m)
 
 
+def gemm_q4_mlx_tensorops_noalloc(rt: Runtime, bank: Q4MlxBank, x_bf16: GpuBuffer, y: GpuBuffer, shape: QuantShape,
+                                  m: int) -> None:
+    """The prefill GEMM for callers that cannot allocate device memory (no counterpart in the
+    reference): intermediate data goes to a fixed 8 MiB array inside the library, larger
+    shapes are refused. See `tessl_gemm_q4_mlx_tensorops_noalloc` in include/tessl_b200.h."""
+    capi.call("tessl_gemm_q4_mlx_tensorops_noalloc", rt.handle, bank.c(), x_bf16.c(), y.c(), shape.c(), m)
+
+
 def gemv_q8(rt: Runtime, packed: GpuBuffer, scales: GpuBuffer, zeros: GpuBuffer, x: GpuBuffer, y: GpuBuffer,
             rows: int, cols: int, group_size: int) -> None:
     """`nn::gemv_q8` (src/nn.rs:716-795)."""
