@@ -76,10 +76,10 @@ def all_gather_rows(local: torch.Tensor, shard: RowShard, m: int = 1, group=None
         padded = local.new_zeros((m, per))
         padded[:, : shard.local_rows] = local
         local = padded
-    gathered = local.new_empty((shard.world, m, per))
+    gathered = local.new_empty((shard.world * m, per))  # rank-major blocks of [m, per]
     dist.all_gather_into_tensor(gathered, local.contiguous(), group=group)
     # [world, m, per] -> [m, world * per] -> first `rows` columns
-    return gathered.permute(1, 0, 2).reshape(m, shard.world * per)[:, : shard.rows].contiguous()
+    return gathered.reshape(shard.world, m, per).permute(1, 0, 2).reshape(m, shard.world * per)[:, : shard.rows].contiguous()
 
 
 def sharded_matvec(compute: Callable[[RowShard], torch.Tensor], rows: int, m: int = 1, group=None,
