@@ -242,6 +242,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     mid_local = torch.empty(layers[0].sh_mid.local_rows, device=dev, dtype=torch.bfloat16)
     mid_full = torch.empty(INTER, device=dev, dtype=torch.bfloat16) if world > 1 else mid_local
     y_local = torch.empty(layers[0].sh_out.local_rows, device=dev)
+    y_full = torch.empty(HIDDEN, device=dev) if world > 1 else y_local
     B = nn.GpuBuffer.from_torch
     bufs = {k: B(v) for k, v in acts.items()}
     qkv_b, o_b, midl_b, midf_b, yl_b = B(qkv_out), B(o_out), B(mid_local), B(mid_full), B(y_local)
@@ -258,12 +259,12 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         nn.gemv_q4_mlx_gate_up_silu(rt, L.gate, L.up, bufs["x_mlp"], midl_b, sg, True)
         if world > 1:
             with torch.cuda.stream(st):
-                mid = sharded.all_gather_rows(mid_local, L.sh_mid)
-                mid_full.copy_(mid.reshape(-1))
+                sharded.all_gather_rows(mid_local, L.sh_mid, out=mid_full)
         nn.gemv_q4_mlx_simd(rt, L.down, midf_b, yl_b, sd)
         if world > 1:
             with torch.cuda.stream(st):
-                return sharded.all_gather_rows(y_local, L.sh_out)
+                sharded.all_gather_rows(y_local, L.sh_out, out=y_full)
+            return y_full
         return y_local
 
     def barrier():
@@ -277,28 +278,22 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         step(i)
     barrier()
 
-    # Launch-bound inner loop: one CUDA graph holds all K steps (single GPU only;
-    # with NCCL in the step the calls are enqueued directly).
-    graph = None
-    if world == 1:
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph, stream=st):
-            for i in range(args.steps):
-                step(i)
-        with torch.cuda.stream(st):
-            graph.replay()
-        barrier()
+    # Launch-bound inner loop: one CUDA graph holds all K steps (kernels and, on
+    # several GPUs, the NCCL all-gathers, captured on the runtime's stream).
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=st):
+        for i in range(args.steps):
+            step(i)
+    with torch.cuda.stream(st):
+        graph.replay()
+    barrier()
 
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with ClockSampler(local_rank) as clocks:
         barrier()
         with torch.cuda.stream(st):
             e0.record(st)
-            if graph is not None:
-                graph.replay()
-            else:
-                for i in range(args.steps):
-                    step(i)
+            graph.replay()
             e1.record(st)
         barrier()
     ms = e0.elapsed_time(e1)

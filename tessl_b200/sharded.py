@@ -63,14 +63,23 @@ def slice_bank(packed: torch.Tensor, scales_biases: torch.Tensor, shard: RowShar
     return packed[shard.begin:shard.end].contiguous(), scales_biases[shard.begin:shard.end].contiguous()
 
 
-def all_gather_rows(local: torch.Tensor, shard: RowShard, m: int = 1, group=None, align: int = 8) -> torch.Tensor:
+def all_gather_rows(local: torch.Tensor, shard: RowShard, m: int = 1, group=None, align: int = 8,
+                    out: "torch.Tensor | None" = None) -> torch.Tensor:
     """All-gather of per-rank outputs `local` [m, local_rows] into [m, rows].
+
+    Fast path: with m == 1 and rows == world * local_rows the slices already sit
+    in output order, so the collective writes straight into `out` (or a new
+    tensor) with no staging copy.
 
     Every rank contributes a slice padded to the common height, the gather is
     one `all_gather_into_tensor`, and the padding is dropped afterwards. With
     m == 1 and rows divisible by world * align no copy is needed beyond the
     collective itself."""
     per = slice_rows_per_rank(shard.rows, shard.world, align)
+    if m == 1 and shard.local_rows == per and per * shard.world == shard.rows:
+        full = out if out is not None else local.new_empty(shard.rows)
+        dist.all_gather_into_tensor(full.reshape(-1), local.reshape(-1), group=group)
+        return full.reshape(1, shard.rows)
     local = local.reshape(m, shard.local_rows)
     if shard.local_rows != per:
         padded = local.new_zeros((m, per))
@@ -79,7 +88,11 @@ def all_gather_rows(local: torch.Tensor, shard: RowShard, m: int = 1, group=None
     gathered = local.new_empty((shard.world * m, per))  # rank-major blocks of [m, per]
     dist.all_gather_into_tensor(gathered, local.contiguous(), group=group)
     # [world, m, per] -> [m, world * per] -> first `rows` columns
-    return gathered.reshape(shard.world, m, per).permute(1, 0, 2).reshape(m, shard.world * per)[:, : shard.rows].contiguous()
+    full = gathered.reshape(shard.world, m, per).permute(1, 0, 2).reshape(m, shard.world * per)[:, : shard.rows]
+    if out is not None:
+        out.reshape(m, shard.rows).copy_(full)
+        return out.reshape(m, shard.rows)
+    return full.contiguous()
 
 
 def sharded_matvec(compute: Callable[[RowShard], torch.Tensor], rows: int, m: int = 1, group=None,
