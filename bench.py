@@ -489,6 +489,49 @@ def cpu_baseline(args):
                       "C/OpenMP (oracle/tessl_oracle.c)", "seconds": round(dt, 2)}
 
 
+def run_case(spec: str):
+    """`--case gemv:N,K[,banks[,iters]]` or `--case prefill:M,N,K[,iters]`: a few plain
+    launches of one operator on seeded banks, for capturing one kernel under ncu."""
+    import torch
+
+    from tessl_b200 import nn
+    kind, _, rest = spec.partition(":")
+    a = [int(v) for v in rest.split(",")]
+    rt = nn.Runtime()
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(1)
+    B = nn.GpuBuffer.from_torch
+
+    def bank(rows, cols):
+        packed = torch.randint(0, 2**31 - 1, (rows, cols // 8), dtype=torch.int32, device="cuda", generator=gen)
+        sc = (torch.rand((rows, cols // GROUP), device="cuda", generator=gen) * 0.018 + 0.002).to(torch.bfloat16)
+        bi = (-8.0 * sc.float() + 0.001 * torch.randn(sc.shape, device="cuda", generator=gen)).to(torch.bfloat16)
+        sb = torch.stack([sc, bi], dim=-1).contiguous()
+        return (packed, sb), nn.Q4MlxBank(B(packed), B(sb))
+
+    if kind == "gemv":
+        n, k = a[0], a[1]
+        nb, iters = (a[2] if len(a) > 2 else 8), (a[3] if len(a) > 3 else 12)
+        keep, banks = zip(*[bank(n, k) for _ in range(nb)])
+        x = torch.randn(k, device="cuda", generator=gen).to(torch.bfloat16)
+        y = torch.empty(n, device="cuda")
+        for i in range(iters):
+            nn.gemv_q4_mlx_simd(rt, banks[i % nb], B(x), B(y), nn.QuantShape(n, k, GROUP))
+    elif kind == "prefill":
+        m, n, k = a[0], a[1], a[2]
+        iters = a[3] if len(a) > 3 else 3
+        keep, bk = bank(n, k)
+        x = torch.randn(m * k, device="cuda", generator=gen).to(torch.bfloat16)
+        y = torch.empty(m * n, device="cuda")
+        for i in range(iters):
+            nn.gemm_q4_mlx_tensorops(rt, bk, B(x), B(y), nn.QuantShape(n, k, GROUP), m)
+    else:
+        raise SystemExit(f"unknown case {spec!r}")
+    rt.synchronize()
+    print(json.dumps({"case": spec, "y0": float(y[0])}))
+    rt.close()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -496,7 +539,11 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-extra", action="store_true", help="skip the other configurations (faster)")
+    ap.add_argument("--case", default=None, help="run a few launches of one operator and exit (for ncu captures)")
     args = ap.parse_args()
+    if args.case:
+        run_case(args.case)
+        return
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
