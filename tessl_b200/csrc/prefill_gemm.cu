@@ -45,112 +45,17 @@
 #include <cuda_fp16.h>
 
 #include <algorithm>
+#include <cstdlib>
 
-#include "q4_gemv_tma.cuh"
-#include "runtime.h"
+#include "prefill_common.cuh"
+#include "prefill_gemm_pair.cuh"
 
 namespace tessl {
 namespace {
 
-using q4k::and_or;
-using q4k::lds128;
-using q4k::mbar_arrive;
-using q4k::mbar_expect_tx;
-using q4k::mbar_init;
-using q4k::mbar_try;
-using q4k::mbar_wait;
-using q4k::smem_u32;
-
-constexpr int BM = 128;  // rows of X per tile = MMA M
-constexpr int BK = 64;   // K block: 128 bytes of f16 = one swizzle row
-constexpr uint32_t kTmemCols = 512;
-
-struct GemmParams {
-    const uint32_t *sb;   // bf16 (scale, bias) pairs [N, K / G]
-    const float *row_scale;  // [M] power-of-two scale removed from each X row
-    void *y;
-    uint32_t M, N, K;
-    uint32_t gshift;       // log2 G
-    uint32_t gpr;          // K / G
-    uint32_t nkb_main;     // ceil(K / 64)
-    uint32_t nkb_extra;    // ceil(4 * gpr / 64)
-    uint32_t tiles_m, tiles_n;
-    int out_bf16;
-    uint32_t *status;
-};
-
-// ---------------------------------------------------------------- PTX wrappers ---
-
-__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, int x, int y, uint32_t bar)
-{
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
-            dst),
-        "l"(map), "r"(x), "r"(y), "r"(bar)
-        : "memory");
-}
-__device__ __forceinline__ void tcgen05_commit(uint32_t bar)
-{
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tcgen05_fence_after()
-{
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-}
-__device__ __forceinline__ void tcgen05_fence_before()
-{
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-}
-/// D[tmem] (+)= A[smem] . B[smem]^T for one K = 16 slice.
-__device__ __forceinline__ void tcgen05_mma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
-                                                uint32_t accumulate)
-{
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(tmem_d),
-        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-/// Shared-memory matrix descriptor: K-major tile, 128-byte swizzle, rows 128 B
-/// apart, 8-row groups 1024 B apart, descriptor version 1 (sm_100).
-__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr)
-{
-    return (uint64_t)((smem_addr & 0x3ffffu) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) |
-           ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
-}
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32])
-{
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,"
-        "%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr));
-}
-__device__ __forceinline__ uint32_t h2_sub(uint32_t a, uint32_t b)
-{
-    uint32_t r;
-    asm("sub.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
-    return r;
-}
-__device__ __forceinline__ uint32_t h2_mul(uint32_t a, uint32_t b)
-{
-    uint32_t r;
-    asm("mul.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
-    return r;
-}
-__device__ __forceinline__ uint32_t h2_fma(uint32_t a, uint32_t b, uint32_t c)
-{
-    uint32_t r;
-    asm("fma.rn.f16x2 %0, %1, %2, %3;" : "=r"(r) : "r"(a), "r"(b), "r"(c));
-    return r;
-}
-__device__ __forceinline__ uint32_t pack_h2(__half lo, __half hi)
-{
-    return (uint32_t)__half_as_ushort(lo) | ((uint32_t)__half_as_ushort(hi) << 16);
-}
+using namespace pf;
+using nn::OutKind;
+using nn::OUT_BF16;
 
 // ------------------------------------------------------- activation pre-pass ---
 
@@ -410,44 +315,12 @@ __global__ void __launch_bounds__(Cfg<BN>::THREADS, 1)
             const uint32_t m = (t % p.tiles_m) * BM + quarter * 32 + lane;
             const uint32_t n0 = (t / p.tiles_m) * BN;
             const float rs = m < p.M ? p.row_scale[m] : 0.0f;
-            const bool vec4 = (p.N & 3u) == 0, vec8 = (p.N & 7u) == 0;
 #pragma unroll 1
             for (uint32_t c = 0; c < BN / 32; ++c) {
                 uint32_t r[32];
                 tmem_ld32(tmem_base + ((quarter * 32u) << 16) + buf * 256u + c * 32u, r);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                const uint32_t n = n0 + c * 32;
-                if (m < p.M && n < p.N) {
-                    if (p.out_bf16) {
-                        uint16_t *dst = static_cast<uint16_t *>(p.y) + (size_t)m * p.N + n;
-                        if (vec8 && n + 32 <= p.N) {
-#pragma unroll
-                            for (int j = 0; j < 4; ++j) {
-                                uint4 o;
-                                uint32_t *ow = &o.x;
-#pragma unroll
-                                for (int k = 0; k < 4; ++k)
-                                    ow[k] = (uint32_t)dev::f32_to_bf16_store(__uint_as_float(r[8 * j + 2 * k]) * rs) |
-                                            ((uint32_t)dev::f32_to_bf16_store(__uint_as_float(r[8 * j + 2 * k + 1]) * rs) << 16);
-                                reinterpret_cast<uint4 *>(dst)[j] = o;
-                            }
-                        } else {
-                            for (uint32_t j = 0; j < 32 && n + j < p.N; ++j)
-                                dst[j] = dev::f32_to_bf16_store(__uint_as_float(r[j]) * rs);
-                        }
-                    } else {
-                        float *dst = static_cast<float *>(p.y) + (size_t)m * p.N + n;
-                        if (vec4 && n + 32 <= p.N) {
-#pragma unroll
-                            for (int j = 0; j < 8; ++j)
-                                reinterpret_cast<float4 *>(dst)[j] =
-                                    make_float4(__uint_as_float(r[4 * j]) * rs, __uint_as_float(r[4 * j + 1]) * rs,
-                                                __uint_as_float(r[4 * j + 2]) * rs, __uint_as_float(r[4 * j + 3]) * rs);
-                        } else {
-                            for (uint32_t j = 0; j < 32 && n + j < p.N; ++j) dst[j] = __uint_as_float(r[j]) * rs;
-                        }
-                    }
-                }
+                store_row32(p, r, m, n0 + c * 32, rs);
             }
             tcgen05_fence_before();
             __syncwarp();
@@ -483,54 +356,13 @@ __global__ void __launch_bounds__(Cfg<BN>::THREADS, 1)
                     if (lane == 0) mbar_arrive(q_empty(sq));  // the packed stage may be refilled
                     ++iq;
                     const uint32_t words[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+                    uint32_t s2[2];
 #pragma unroll
-                    for (int h = 0; h < 2; ++h) {
-                        const uint32_t g = min((kb * 64 + h * 32) >> p.gshift, p.gpr - 1);
-                        const float sc = dev::bf16_lo(__ldg(sbrow + g));
-                        const __half sh = __float2half_rn(sc);
-                        const uint32_t s2 = pack_h2(sh, sh);
-#pragma unroll
-                        for (int c4 = 0; c4 < 4; ++c4) {
-                            const uint32_t w = words[4 * h + c4], w8 = w >> 8;
-                            // (1024 + q) and (1024 + 16 q) as f16 pairs, then q - 8 exactly, then * s exactly
-                            const uint32_t t0 = and_or(w, 0x000f000fu, 0x64006400u);
-                            const uint32_t t1 = and_or(w, 0x00f000f0u, 0x64006400u);
-                            const uint32_t t2 = and_or(w8, 0x000f000fu, 0x64006400u);
-                            const uint32_t t3 = and_or(w8, 0x00f000f0u, 0x64006400u);
-                            uint4 o;
-                            o.x = h2_mul(h2_sub(t0, 0x64086408u), s2);                // 1024 + q - 1032
-                            o.y = h2_mul(h2_fma(t1, 0x2c002c00u, 0xd480d480u), s2);  // (1024 + 16 q) / 16 - 72
-                            o.z = h2_mul(h2_sub(t2, 0x64086408u), s2);
-                            o.w = h2_mul(h2_fma(t3, 0x2c002c00u, 0xd480d480u), s2);
-                            const uint32_t c = 4 * h + c4;
-                            asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(brow + ((c << 4) ^ swz)), "r"(o.x),
-                                         "r"(o.y), "r"(o.z), "r"(o.w)
-                                         : "memory");
-                        }
-                    }
+                    for (int h = 0; h < 2; ++h)
+                        s2[h] = scale_h2(__ldg(sbrow + min((kb * 64 + h * 32) >> p.gshift, p.gpr - 1)));
+                    expand_q4_block(words, s2, brow, swz);
                 } else {
-                    // extra K block: (c1, c1, c1, c2) per group, c1 + c2 = b + 8 s in two f16 pieces
-                    const uint32_t e = kb - p.nkb_main;
-#pragma unroll
-                    for (int c = 0; c < 8; ++c) {
-                        uint32_t o[4];
-#pragma unroll
-                        for (int j = 0; j < 2; ++j) {
-                            const uint32_t g = e * 16 + 2 * c + j;
-                            uint32_t lo = 0, hi = 0;
-                            if (g < p.gpr) {
-                                const uint32_t pair = __ldg(sbrow + g);
-                                const float bp = fmaf(8.0f, dev::bf16_lo(pair), dev::bf16_hi(pair));
-                                const __half c1 = __float2half_rn(bp);
-                                const __half c2 = __float2half_rn(bp - __half2float(c1));
-                                lo = pack_h2(c1, c1), hi = pack_h2(c1, c2);
-                            }
-                            o[2 * j] = lo, o[2 * j + 1] = hi;
-                        }
-                        asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(brow + (((uint32_t)c << 4) ^ swz)),
-                                     "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3])
-                                     : "memory");
-                    }
+                    expand_extra_block(sbrow, kb - p.nkb_main, p.gpr, brow, swz);
                 }
                 // generic-proxy stores -> visible to the tensor core's async-proxy reads
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -595,7 +427,6 @@ Result launch_gemm(TesslRuntime *rt, const CUtensorMap &ma, const CUtensorMap &m
                              "gemm_q4_mlx_tensorops: shared memory opt-in"));
         opted = true;
     }
-    p.tiles_n = (p.N + BN - 1) / BN;
     const uint32_t tiles = p.tiles_m * p.tiles_n;
     const uint32_t grid = std::min<uint32_t>(tiles, (uint32_t)rt->sm_count);
     kernel<<<grid, C::THREADS, C::SMEM, rt->stream>>>(ma, mw, p);
@@ -603,20 +434,37 @@ Result launch_gemm(TesslRuntime *rt, const CUtensorMap &ma, const CUtensorMap &m
     return cuda_check(rt, cudaGetLastError(), "gemm_q4_mlx_tensorops launch");
 }
 
-}  // namespace
-
-namespace nn {
-
-uint32_t gemm_q4_mlx_tensorops_max_k(uint32_t m, uint32_t n, uint32_t group_size)
+/// The CTA-pair kernel: one cluster of two CTAs per pair of SMs, persistent over 256 x BN tiles.
+template <int BN>
+Result launch_gemm_pair(TesslRuntime *rt, const CUtensorMap &ma, const CUtensorMap &mw, GemmParams p)
 {
-    const uint64_t widest = std::max<uint64_t>(std::max(m, n), 1);
-    const uint64_t k = std::min<uint64_t>(0x7fffffffull / widest, 0xffffffffull);
-    const uint64_t g = std::max<uint32_t>(group_size, 1);
-    return (uint32_t)(k / g * g);
+    using C = PairCfg<BN>;
+    auto kernel = q4_prefill_gemm_pair_kernel<BN>;
+    static bool opted = false;
+    if (!opted) {
+        TESSL_TRY(cuda_check(rt, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM),
+                             "gemm_q4_mlx_tensorops: shared memory opt-in"));
+        opted = true;
+    }
+    const uint32_t tiles = p.tiles_m * p.tiles_n;
+    const uint32_t clusters = std::min<uint32_t>(tiles, (uint32_t)rt->sm_count / 2);
+    kernel<<<2 * clusters, C::THREADS, C::SMEM, rt->stream>>>(ma, mw, p);
+    rt->dispatch_count += 1;
+    return cuda_check(rt, cudaGetLastError(), "gemm_q4_mlx_tensorops launch");
 }
 
-Result gemm_q4_mlx_tensorops(TesslRuntime *rt, const TesslQ4MlxBank &bank, const TesslBuf &x_bf16, const TesslBuf &y,
-                             const TesslQuantShape &shape, uint32_t m, OutKind out)
+/// Shapes and scratch layout of one prefill GEMM call.
+struct PrefillPlan {
+    uint32_t n, k, groups, gshift, nkb_main, nkb_extra, k64, k_aug;
+    size_t a_bytes;  // augmented f16 activations [m, k_aug], rounded up to 256 bytes
+    size_t need;     // a_bytes + m row scales
+};
+
+/// Argument checks shared by the allocating and the non-allocating entry, in the
+/// reference's order (src/nn.rs:4697-4740 of the reference project). `*empty` is
+/// set when there is nothing to compute.
+Result prefill_validate(const TesslQ4MlxBank &bank, const TesslBuf &x_bf16, const TesslBuf &y,
+                        const TesslQuantShape &shape, uint32_t m, OutKind out, PrefillPlan *plan, bool *empty)
 {
     const char *what = "gemm_q4_mlx_tensorops";
     TESSL_TRY(quant_shape_validate(shape, what));
@@ -639,70 +487,100 @@ Result gemm_q4_mlx_tensorops(TesslRuntime *rt, const TesslQ4MlxBank &bank, const
     const Named writes[] = {{"y", &y}};
     const Named reads[] = {{"packed", &bank.packed}, {"scales_biases", &bank.scales_biases}, {"x_bf16", &x_bf16}};
     TESSL_TRY(require_disjoint_writes(what, writes, 1, reads, 3));
-    if (m == 0 || n == 0) return ok();
+    *empty = m == 0 || n == 0;
+    if (*empty) return ok();
     TESSL_TRY(require_aligned16(bank.packed, std::string(what) + " packed"));
     TESSL_TRY(require_aligned16(x_bf16, std::string(what) + " x_bf16"));
     TESSL_TRY(require_aligned16(y, std::string(what) + " y"));
     if (((uintptr_t)bank.scales_biases.ptr & 3u) != 0)
         return fmt("%s scales_biases: device pointer must be 4-byte aligned", what);
 
-    uint32_t gshift = 0;
-    while ((1u << gshift) < shape.group_size) ++gshift;
-    const uint32_t nkb_main = (k + BK - 1) / BK;
-    const uint32_t nkb_extra = (4 * groups + BK - 1) / BK;
-    const uint32_t k64 = nkb_main * BK, k_aug = (nkb_main + nkb_extra) * BK;
+    PrefillPlan pl{};
+    pl.n = n, pl.k = k, pl.groups = groups;
+    while ((1u << pl.gshift) < shape.group_size) ++pl.gshift;
+    pl.nkb_main = (k + BK - 1) / BK;
+    pl.nkb_extra = (4 * groups + BK - 1) / BK;
+    pl.k64 = pl.nkb_main * BK, pl.k_aug = (pl.nkb_main + pl.nkb_extra) * BK;
+    pl.a_bytes = ((size_t)m * pl.k_aug * 2 + 255) & ~(size_t)255;
+    pl.need = pl.a_bytes + (size_t)m * 4;
+    *plan = pl;
+    return ok();
+}
 
-    // Scratch: the augmented f16 activations [m, k_aug] and the row scales [m].
-    const size_t a_bytes = ((size_t)m * k_aug * 2 + 255) & ~(size_t)255;
-    void *scratch = nullptr;
-    TESSL_TRY(scratch_reserve(rt, a_bytes + (size_t)m * 4, &scratch));
-    __half *a_aug = static_cast<__half *>(scratch);
-    float *row_scale = reinterpret_cast<float *>(static_cast<char *>(scratch) + a_bytes);
-
-    x_prepare_kernel<<<m, 256, 0, rt->stream>>>(static_cast<const uint16_t *>(x_bf16.ptr), a_aug, row_scale, k, k64,
-                                                k_aug, gshift);
-    rt->dispatch_count += 1;
-    TESSL_TRY(cuda_check(rt, cudaGetLastError(), "gemm_q4_mlx_tensorops pre-pass launch"));
-
-    // Tile width: fewest (waves x width), i.e. least time lost in a partial last wave.
-    const uint32_t tiles_m = (m + BM - 1) / BM;
+/// Tile width with the least time lost in a partial last wave: fewest (waves x width).
+int pick_tile_width(uint64_t tiles_m, uint32_t n, uint32_t slots)
+{
     int best_bn = 256;
     uint64_t best_cost = ~0ull;
     for (int bn : {256, 192, 128}) {
-        const uint64_t tiles = (uint64_t)tiles_m * ((n + bn - 1) / bn);
-        const uint64_t waves = (tiles + rt->sm_count - 1) / rt->sm_count;
+        const uint64_t tiles = tiles_m * ((n + bn - 1) / bn);
+        const uint64_t waves = (tiles + slots - 1) / slots;
         const uint64_t cost = waves * (uint64_t)bn;
         if (cost < best_cost) best_cost = cost, best_bn = bn;
     }
+    return best_bn;
+}
+
+/// 0 = single-CTA kernel only, 1 = CTA-pair kernel whenever there are at least two
+/// 128-row blocks (the default), from TESSL_B200_PREFILL_PAIR.
+int pair_mode()
+{
+    static int mode = -1;
+    if (mode < 0) {
+        const char *e = std::getenv("TESSL_B200_PREFILL_PAIR");
+        mode = (e && e[0] == '0') ? 0 : 1;
+    }
+    return mode;
+}
+
+/// Pre-pass and GEMM of a validated call; `scratch` holds `plan.need` bytes.
+Result prefill_launch(TesslRuntime *rt, const TesslQ4MlxBank &bank, const TesslBuf &x_bf16, const TesslBuf &y, uint32_t m,
+                      OutKind out, const PrefillPlan &pl, void *scratch)
+{
+    __half *a_aug = static_cast<__half *>(scratch);
+    float *row_scale = reinterpret_cast<float *>(static_cast<char *>(scratch) + pl.a_bytes);
+    x_prepare_kernel<<<m, 256, 0, rt->stream>>>(static_cast<const uint16_t *>(x_bf16.ptr), a_aug, row_scale, pl.k, pl.k64,
+                                                pl.k_aug, pl.gshift);
+    rt->dispatch_count += 1;
+    TESSL_TRY(cuda_check(rt, cudaGetLastError(), "gemm_q4_mlx_tensorops pre-pass launch"));
+
+    const bool pair = pair_mode() != 0 && m > BM && rt->sm_count >= 2;
+    const uint32_t tiles_m = pair ? (m + 2 * BM - 1) / (2 * BM) : (m + BM - 1) / BM;
+    const int bn = pick_tile_width(tiles_m, pl.n, pair ? (uint32_t)rt->sm_count / 2 : (uint32_t)rt->sm_count);
 
     EncodeTiled enc = nullptr;
     TESSL_TRY(tensormap_encoder(rt, &enc));
     CUtensorMap ma, mw;
-    TESSL_TRY(make_map_2d(enc, &ma, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, a_aug, k_aug, m, (uint64_t)k_aug * 2, BK, BM,
+    TESSL_TRY(make_map_2d(enc, &ma, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, a_aug, pl.k_aug, m, (uint64_t)pl.k_aug * 2, BK, BM,
                           CU_TENSOR_MAP_SWIZZLE_128B));
-    TESSL_TRY(make_map_2d(enc, &mw, CU_TENSOR_MAP_DATA_TYPE_UINT8, bank.packed.ptr, k / 2, n, k / 2, 32,
-                          (uint32_t)best_bn, CU_TENSOR_MAP_SWIZZLE_NONE));
+    // Packed weights: 32 bytes of BN rows (single CTA) or of this CTA's BN/2 rows (pair) per K block.
+    TESSL_TRY(make_map_2d(enc, &mw, CU_TENSOR_MAP_DATA_TYPE_UINT8, bank.packed.ptr, pl.k / 2, pl.n, pl.k / 2, 32,
+                          (uint32_t)(pair ? bn / 2 : bn), CU_TENSOR_MAP_SWIZZLE_NONE));
 
     GemmParams p{};
     p.sb = static_cast<const uint32_t *>(bank.scales_biases.ptr);
     p.row_scale = row_scale;
     p.y = y.ptr;
-    p.M = m, p.N = n, p.K = k;
-    p.gshift = gshift, p.gpr = groups;
-    p.nkb_main = nkb_main, p.nkb_extra = nkb_extra;
+    p.M = m, p.N = pl.n, p.K = pl.k;
+    p.gshift = pl.gshift, p.gpr = pl.groups;
+    p.nkb_main = pl.nkb_main, p.nkb_extra = pl.nkb_extra;
     p.tiles_m = tiles_m;
+    p.tiles_n = (pl.n + bn - 1) / bn;
     p.out_bf16 = out == OUT_BF16;
     p.status = rt->status_dev;
-    if (best_bn == 256) return launch_gemm<256>(rt, ma, mw, p);
-    if (best_bn == 192) return launch_gemm<192>(rt, ma, mw, p);
+#ifdef TESSL_GEMM_TIMING
+    p.timing = nullptr;
+    if (const char *e = std::getenv("TESSL_B200_TIMING_PTR")) p.timing = (long long *)std::strtoull(e, nullptr, 0);
+#endif
+    if (pair) {
+        if (bn == 256) return launch_gemm_pair<256>(rt, ma, mw, p);
+        if (bn == 192) return launch_gemm_pair<192>(rt, ma, mw, p);
+        return launch_gemm_pair<128>(rt, ma, mw, p);
+    }
+    if (bn == 256) return launch_gemm<256>(rt, ma, mw, p);
+    if (bn == 192) return launch_gemm<192>(rt, ma, mw, p);
     return launch_gemm<128>(rt, ma, mw, p);
 }
-
-}  // namespace nn
-
-// ------------------------------------------- prefill GEMM without allocation ---
-
-namespace {
 
 /// Upper bound of the built-in scratch: enough for m * K_aug f16 activations plus
 /// m row scales, e.g. 512 rows at K = 4096, G = 64, or 2048 rows at K = 1024.
@@ -740,6 +618,27 @@ Result static_scratch_address(TesslRuntime *rt, void **out)
 
 namespace nn {
 
+uint32_t gemm_q4_mlx_tensorops_max_k(uint32_t m, uint32_t n, uint32_t group_size)
+{
+    const uint64_t widest = std::max<uint64_t>(std::max(m, n), 1);
+    const uint64_t k = std::min<uint64_t>(0x7fffffffull / widest, 0xffffffffull);
+    const uint64_t g = std::max<uint32_t>(group_size, 1);
+    return (uint32_t)(k / g * g);
+}
+
+Result gemm_q4_mlx_tensorops(TesslRuntime *rt, const TesslQ4MlxBank &bank, const TesslBuf &x_bf16, const TesslBuf &y,
+                             const TesslQuantShape &shape, uint32_t m, OutKind out)
+{
+    PrefillPlan pl{};
+    bool empty = false;
+    TESSL_TRY(prefill_validate(bank, x_bf16, y, shape, m, out, &pl, &empty));
+    if (empty) return ok();
+    // Scratch: the augmented f16 activations [m, k_aug] and the row scales [m].
+    void *scratch = nullptr;
+    TESSL_TRY(scratch_reserve(rt, pl.need, &scratch));
+    return prefill_launch(rt, bank, x_bf16, y, m, out, pl, scratch);
+}
+
 /// `gemm_q4_mlx_tensorops` for callers that must not allocate device memory
 /// while they run: serving loops that forbid anything that can synchronise the
 /// device or fail for lack of memory in steady state, code inside another
@@ -759,83 +658,18 @@ namespace nn {
 Result gemm_q4_mlx_tensorops_noalloc(TesslRuntime *rt, const TesslQ4MlxBank &bank, const TesslBuf &x_bf16,
                                      const TesslBuf &y, const TesslQuantShape &shape, uint32_t m, OutKind out)
 {
-    const char *what = "gemm_q4_mlx_tensorops";
-    TESSL_TRY(quant_shape_validate(shape, what));
-    if (shape.group_size != 32 && shape.group_size != 64 && shape.group_size != 128) {
-        return fmt("%s: group_size %u is not one of [32, 64, 128]; the matmul2d descriptor's K is the group, so each "
-                   "size is its own entry point",
-                   what, shape.group_size);
-    }
-    if (shape.cols == 0) return fmt("%s: cols must be non-zero", what);
-    const uint32_t n = shape.rows, k = shape.cols, groups = k / shape.group_size;
-    TESSL_TRY(require_i32_extent(elems(m, k), "gemm_q4_mlx_tensorops x (m * cols)"));
-    TESSL_TRY(require_i32_extent(elems(n, k), "gemm_q4_mlx_tensorops weights (rows * cols 4-bit elements)"));
-    TESSL_TRY(require_i32_extent(elems(m, n), "gemm_q4_mlx_tensorops y (m * rows)"));
-    TESSL_TRY(require_i32_extent(elems(n, groups), "gemm_q4_mlx_tensorops scale/bias pairs (rows * groups)"));
-    TESSL_TRY(q4_bank_validate(bank, shape, what));
-    TESSL_TRY(require(x_bf16, elems(m, k), 2, std::string(what) + " x_bf16"));
-    TESSL_TRY(require(y, elems(m, n), out == OUT_BF16 ? 2 : 4, std::string(what) + " y"));
-    const Named writes[] = {{"y", &y}};
-    const Named reads[] = {{"packed", &bank.packed}, {"scales_biases", &bank.scales_biases}, {"x_bf16", &x_bf16}};
-    TESSL_TRY(require_disjoint_writes(what, writes, 1, reads, 3));
-    if (m == 0 || n == 0) return ok();
-    TESSL_TRY(require_aligned16(bank.packed, std::string(what) + " packed"));
-    TESSL_TRY(require_aligned16(x_bf16, std::string(what) + " x_bf16"));
-    TESSL_TRY(require_aligned16(y, std::string(what) + " y"));
-    if (((uintptr_t)bank.scales_biases.ptr & 3u) != 0)
-        return fmt("%s scales_biases: device pointer must be 4-byte aligned", what);
-
-    uint32_t gshift = 0;
-    while ((1u << gshift) < shape.group_size) ++gshift;
-    const uint32_t nkb_main = (k + BK - 1) / BK;
-    const uint32_t nkb_extra = (4 * groups + BK - 1) / BK;
-    const uint32_t k64 = nkb_main * BK, k_aug = (nkb_main + nkb_extra) * BK;
-    const size_t a_bytes = ((size_t)m * k_aug * 2 + 255) & ~(size_t)255;
-    const size_t need = a_bytes + (size_t)m * 4;
-    if (need > kStaticScratchBytes) {
+    PrefillPlan pl{};
+    bool empty = false;
+    TESSL_TRY(prefill_validate(bank, x_bf16, y, shape, m, out, &pl, &empty));
+    if (empty) return ok();
+    if (pl.need > kStaticScratchBytes) {
         return fmt("gemm_q4_mlx_tensorops_noalloc: m = %u rows of %u columns need %zu bytes of scratch but the "
                    "built-in scratch holds %zu; use gemm_q4_mlx_tensorops, which allocates",
-                   m, k, need, kStaticScratchBytes);
+                   m, pl.k, pl.need, kStaticScratchBytes);
     }
     void *scratch = nullptr;
     TESSL_TRY(static_scratch_address(rt, &scratch));
-    __half *a_aug = static_cast<__half *>(scratch);
-    float *row_scale = reinterpret_cast<float *>(static_cast<char *>(scratch) + a_bytes);
-
-    x_prepare_kernel<<<m, 256, 0, rt->stream>>>(static_cast<const uint16_t *>(x_bf16.ptr), a_aug, row_scale, k, k64,
-                                                k_aug, gshift);
-    rt->dispatch_count += 1;
-    TESSL_TRY(cuda_check(rt, cudaGetLastError(), "gemm_q4_mlx_tensorops pre-pass launch"));
-
-    const uint32_t tiles_m = (m + BM - 1) / BM;
-    int best_bn = 256;
-    uint64_t best_cost = ~0ull;
-    for (int bn : {256, 192, 128}) {
-        const uint64_t tiles = (uint64_t)tiles_m * ((n + bn - 1) / bn);
-        const uint64_t waves = (tiles + rt->sm_count - 1) / rt->sm_count;
-        const uint64_t cost = waves * (uint64_t)bn;
-        if (cost < best_cost) best_cost = cost, best_bn = bn;
-    }
-    EncodeTiled enc = nullptr;
-    TESSL_TRY(tensormap_encoder(rt, &enc));
-    CUtensorMap ma, mw;
-    TESSL_TRY(make_map_2d(enc, &ma, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, a_aug, k_aug, m, (uint64_t)k_aug * 2, BK, BM,
-                          CU_TENSOR_MAP_SWIZZLE_128B));
-    TESSL_TRY(make_map_2d(enc, &mw, CU_TENSOR_MAP_DATA_TYPE_UINT8, bank.packed.ptr, k / 2, n, k / 2, 32,
-                          (uint32_t)best_bn, CU_TENSOR_MAP_SWIZZLE_NONE));
-    GemmParams p{};
-    p.sb = static_cast<const uint32_t *>(bank.scales_biases.ptr);
-    p.row_scale = row_scale;
-    p.y = y.ptr;
-    p.M = m, p.N = n, p.K = k;
-    p.gshift = gshift, p.gpr = groups;
-    p.nkb_main = nkb_main, p.nkb_extra = nkb_extra;
-    p.tiles_m = tiles_m;
-    p.out_bf16 = out == OUT_BF16;
-    p.status = rt->status_dev;
-    if (best_bn == 256) return launch_gemm<256>(rt, ma, mw, p);
-    if (best_bn == 192) return launch_gemm<192>(rt, ma, mw, p);
-    return launch_gemm<128>(rt, ma, mw, p);
+    return prefill_launch(rt, bank, x_bf16, y, m, out, pl, scratch);
 }
 
 }  // namespace nn

@@ -78,6 +78,20 @@ def test_sweep_within_the_derived_bound(rt, group, random):
 
 
 @pytest.mark.parametrize("group", [32, 64, 128])
+def test_two_cta_tiles(rt, group):
+    """More than 128 rows of X: the CTA-pair kernel (256-row tiles, each CTA expanding half
+    of the weight rows), with ragged last tiles in both directions."""
+    for m in (129, 256, 300):
+        for n in (64, 100, 257, 520):
+            for k in (256, 384):
+                x, packed, sb = ref_case(m, n, k, group, True, seed_salt=0x2C7A)
+                got = run_gemm(rt, x, packed, sb, m, n, k, group)
+                assert np.all(got != SENTINEL_F32), f"unwritten output M={m} N={n} K={k} G={group}"
+                assert_gamma_bound(got, packed, sb, x, m, n, k, group, extra_terms=group,
+                                   what=f"pair M={m} N={n} K={k} G={group}")
+
+
+@pytest.mark.parametrize("group", [32, 64, 128])
 def test_long_k(rt, group):
     m, n, k = 40, 72, 2048
     x, packed, sb = ref_case(m, n, k, group, True)
@@ -88,7 +102,7 @@ def test_long_k(rt, group):
 @pytest.mark.parametrize("group", [32, 64, 128])
 def test_partial_tiles_never_write_past_y(rt, group):
     pad = 32 * 32 + 128
-    for m in (1, 8, 33, 70, 129):
+    for m in (1, 8, 33, 70, 129, 257):
         for n in (33, 40, 100, 257):
             x, packed, sb = ref_case(m, n, 256, group, True, seed_salt=0x9AD)
             for as_bf16 in (False, True):
