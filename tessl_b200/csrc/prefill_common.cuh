@@ -130,17 +130,18 @@ __device__ __forceinline__ uint32_t pack_h2(__half lo, __half hi)
 
 // ------------------------------------------------- weight expansion, stores ---
 
-/// Eight packed words (64 nibbles of one weight row, K block `kb`) -> 64 f16 values
-/// s * (q - 8), written as eight 16-byte chunks of the 128-byte row at `brow`
-/// with the 128B swizzle (`swz` = (row & 7) << 4). `s2[h]` is the group scale of
-/// the block's half h as an f16 pair. Each 16-byte chunk holds the eight weights
-/// of one packed word in the order 0,4,1,5,2,6,3,7.
-__device__ __forceinline__ void expand_q4_block(const uint32_t (&words)[8], const uint32_t (&s2)[2], uint32_t brow,
-                                                uint32_t swz)
+/// NW packed words (8 nibbles each) of one weight row -> 8 NW f16 values
+/// s * (q - 8), written as 16-byte chunks c0 .. c0 + NW - 1 of the 128-byte row at
+/// `brow` with the 128B swizzle (`swz` = (row & 7) << 4). `s` is the group scale
+/// as an f16 pair. Each chunk holds the eight weights of one packed word in the
+/// order 0,4,1,5,2,6,3,7.
+template <int NW>
+__device__ __forceinline__ void expand_q4_words(const uint32_t (&words)[NW], uint32_t s, uint32_t brow, uint32_t swz,
+                                                uint32_t c0)
 {
 #pragma unroll
-    for (int c = 0; c < 8; ++c) {
-        const uint32_t w = words[c], w8 = w >> 8, s = s2[c >> 2];
+    for (int c = 0; c < NW; ++c) {
+        const uint32_t w = words[c], w8 = w >> 8;
         // (1024 + q) and (1024 + 16 q) as f16 pairs, then q - 8 exactly, then * s exactly
         const uint32_t t0 = and_or(w, 0x000f000fu, 0x64006400u);
         const uint32_t t1 = and_or(w, 0x00f000f0u, 0x64006400u);
@@ -150,8 +151,8 @@ __device__ __forceinline__ void expand_q4_block(const uint32_t (&words)[8], cons
         const uint32_t oy = h2_mul(h2_fma(t1, 0x2c002c00u, 0xd480d480u), s);  // (1024 + 16 q) / 16 - 72
         const uint32_t oz = h2_mul(h2_sub(t2, 0x64086408u), s);
         const uint32_t ow = h2_mul(h2_fma(t3, 0x2c002c00u, 0xd480d480u), s);
-        asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(brow + (((uint32_t)c << 4) ^ swz)), "r"(ox), "r"(oy),
-                     "r"(oz), "r"(ow)
+        asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(brow + (((c0 + (uint32_t)c) << 4) ^ swz)), "r"(ox),
+                     "r"(oy), "r"(oz), "r"(ow)
                      : "memory");
     }
 }
@@ -163,13 +164,16 @@ __device__ __forceinline__ uint32_t scale_h2(uint32_t pair)
     return pack_h2(sh, sh);
 }
 
-/// Extra K block `e` of one weight row: per group (c1, c1, c1, c2) with c1 + c2 the
-/// two-piece f16 split of b + 8 s; groups past `gpr` are zero.
-__device__ __forceinline__ void expand_extra_block(const uint32_t *sbrow, uint32_t e, uint32_t gpr, uint32_t brow,
-                                                   uint32_t swz)
+/// Chunks c0 .. c0 + NC - 1 of extra K block `e` of one weight row: per group
+/// (c1, c1, c1, c2) with c1 + c2 the two-piece f16 split of b + 8 s, two groups
+/// per chunk; groups past `gpr` are zero.
+template <int NC>
+__device__ __forceinline__ void expand_extra_chunks(const uint32_t *sbrow, uint32_t e, uint32_t gpr, uint32_t brow,
+                                                    uint32_t swz, uint32_t c0)
 {
 #pragma unroll
-    for (int c = 0; c < 8; ++c) {
+    for (int cc = 0; cc < NC; ++cc) {
+        const uint32_t c = c0 + (uint32_t)cc;
         uint32_t o[4];
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
@@ -184,8 +188,8 @@ __device__ __forceinline__ void expand_extra_block(const uint32_t *sbrow, uint32
             }
             o[2 * j] = lo, o[2 * j + 1] = hi;
         }
-        asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(brow + (((uint32_t)c << 4) ^ swz)), "r"(o[0]), "r"(o[1]),
-                     "r"(o[2]), "r"(o[3])
+        asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(brow + ((c << 4) ^ swz)), "r"(o[0]), "r"(o[1]), "r"(o[2]),
+                     "r"(o[3])
                      : "memory");
     }
 }
@@ -226,6 +230,62 @@ __device__ __forceinline__ void store_row32(const GemmParams &p, const uint32_t 
             for (uint32_t j = 0; j < 32; ++j)
                 if (n + j < p.N) dst[j] = __uint_as_float(r[j]) * rs;
         }
+    }
+}
+
+/// The same 32 x 32 block of outputs as 32 calls of store_row32 (lane = row
+/// m_base + lane, columns n .. n + 31), but written with full 128-byte lines: the
+/// warp transposes the block through `stage` (4 KiB of shared memory of its own,
+/// 16-byte chunks XOR-swizzled so both phases are bank-conflict free) and each
+/// store instruction then covers whole rows segments instead of 32 scattered
+/// 16-byte pieces. Falls back to the per-row path for ragged widths.
+__device__ __forceinline__ void store_block32_coalesced(const GemmParams &p, const uint32_t (&r)[32], uint32_t stage,
+                                                        uint32_t lane, uint32_t m_base, uint32_t n, float rs)
+{
+    if (n >= p.N) return;
+    if (!p.out_bf16 && (p.N & 3u) == 0 && n + 32 <= p.N) {
+#pragma unroll
+        for (uint32_t j = 0; j < 8; ++j) {
+            const uint32_t a = stage + lane * 128 + ((j ^ (lane & 7u)) << 4);
+            asm volatile("st.shared.v4.f32 [%0], {%1,%2,%3,%4};" ::"r"(a), "f"(__uint_as_float(r[4 * j]) * rs),
+                         "f"(__uint_as_float(r[4 * j + 1]) * rs), "f"(__uint_as_float(r[4 * j + 2]) * rs),
+                         "f"(__uint_as_float(r[4 * j + 3]) * rs)
+                         : "memory");
+        }
+        __syncwarp();
+        const uint32_t cj = lane & 7u, rsub = lane >> 3;
+        float *y = static_cast<float *>(p.y);
+#pragma unroll
+        for (uint32_t i = 0; i < 8; ++i) {
+            const uint32_t row = 4 * i + rsub;
+            const uint4 v = lds128(stage + row * 128 + ((cj ^ (row & 7u)) << 4));
+            if (m_base + row < p.M) *reinterpret_cast<uint4 *>(y + (size_t)(m_base + row) * p.N + n + 4 * cj) = v;
+        }
+        __syncwarp();
+    } else if (p.out_bf16 && (p.N & 7u) == 0 && n + 32 <= p.N) {
+#pragma unroll
+        for (uint32_t j = 0; j < 4; ++j) {
+            uint32_t o[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+                o[k] = (uint32_t)dev::f32_to_bf16_store(__uint_as_float(r[8 * j + 2 * k]) * rs) |
+                       ((uint32_t)dev::f32_to_bf16_store(__uint_as_float(r[8 * j + 2 * k + 1]) * rs) << 16);
+            const uint32_t a = stage + lane * 64 + ((j ^ ((lane >> 1) & 3u)) << 4);
+            asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(a), "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3])
+                         : "memory");
+        }
+        __syncwarp();
+        const uint32_t cj = lane & 3u, rsub = lane >> 2;
+        uint16_t *y = static_cast<uint16_t *>(p.y);
+#pragma unroll
+        for (uint32_t i = 0; i < 4; ++i) {
+            const uint32_t row = 8 * i + rsub;
+            const uint4 v = lds128(stage + row * 64 + ((cj ^ ((row >> 1) & 3u)) << 4));
+            if (m_base + row < p.M) *reinterpret_cast<uint4 *>(y + (size_t)(m_base + row) * p.N + n + 8 * cj) = v;
+        }
+        __syncwarp();
+    } else {
+        store_row32(p, r, m_base + lane, n, rs);
     }
 }
 
@@ -287,6 +347,36 @@ __device__ __forceinline__ void tcgen05_commit_pair(uint32_t bar)
     asm volatile(
         "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar),
         "h"(mask)
+        : "memory");
+}
+
+/// Position in a ring of S stages with the parity of its current round; advancing
+/// wraps without a division (the role loops run once per K block).
+template <int S>
+struct RingPos {
+    uint32_t stage = 0, phase = 0;
+    __device__ __forceinline__ void advance(uint32_t n = 1)  // n <= S
+    {
+        stage += n;
+        if (stage >= (uint32_t)S) stage -= (uint32_t)S, phase ^= 1u;
+    }
+    __device__ __forceinline__ void set(uint32_t index) { stage = index % (uint32_t)S, phase = (index / (uint32_t)S) & 1u; }
+};
+
+/// Low word of the shared-memory matrix descriptor of a K-major, 128B-swizzled
+/// tile at `smem_addr`; the high word is kUmmaDescHi for every such tile.
+__device__ __forceinline__ uint32_t umma_desc_lo(uint32_t smem_addr) { return ((smem_addr & 0x3ffffu) >> 4) | (1u << 16); }
+constexpr uint32_t kUmmaDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);
+
+/// Pair MMA with the descriptors given by their low words.
+__device__ __forceinline__ void tcgen05_mma_f16_pair_lo(uint32_t tmem_d, uint32_t adesc_lo, uint32_t bdesc_lo, uint32_t idesc,
+                                                        uint32_t accumulate)
+{
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "mov.b64 da, {%1, %5};\n\tmov.b64 db, {%2, %5};\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %3, p;\n\t}" ::"r"(tmem_d),
+        "r"(adesc_lo), "r"(bdesc_lo), "r"(idesc), "r"(accumulate), "r"(kUmmaDescHi)
         : "memory");
 }
 

@@ -355,14 +355,13 @@ __global__ void __launch_bounds__(Cfg<BN>::THREADS, 1)
                     __syncwarp();
                     if (lane == 0) mbar_arrive(q_empty(sq));  // the packed stage may be refilled
                     ++iq;
-                    const uint32_t words[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
-                    uint32_t s2[2];
-#pragma unroll
-                    for (int h = 0; h < 2; ++h)
-                        s2[h] = scale_h2(__ldg(sbrow + min((kb * 64 + h * 32) >> p.gshift, p.gpr - 1)));
-                    expand_q4_block(words, s2, brow, swz);
+                    const uint32_t lo[4] = {w0.x, w0.y, w0.z, w0.w}, hi[4] = {w1.x, w1.y, w1.z, w1.w};
+                    const uint32_t g0 = min((kb * 64) >> p.gshift, p.gpr - 1);
+                    const uint32_t g1 = min((kb * 64 + 32) >> p.gshift, p.gpr - 1);
+                    expand_q4_words<4>(lo, scale_h2(__ldg(sbrow + g0)), brow, swz, 0);
+                    expand_q4_words<4>(hi, scale_h2(__ldg(sbrow + g1)), brow, swz, 4);
                 } else {
-                    expand_extra_block(sbrow, kb - p.nkb_main, p.gpr, brow, swz);
+                    expand_extra_chunks<8>(sbrow, kb - p.nkb_main, p.gpr, brow, swz, 0);
                 }
                 // generic-proxy stores -> visible to the tensor core's async-proxy reads
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -507,15 +506,24 @@ Result prefill_validate(const TesslQ4MlxBank &bank, const TesslBuf &x_bf16, cons
     return ok();
 }
 
-/// Tile width with the least time lost in a partial last wave: fewest (waves x width).
+/// Tile width with the least estimated time: waves of tiles x the cost of one tile's K block.
 int pick_tile_width(uint64_t tiles_m, uint32_t n, uint32_t slots)
 {
+    // TESSL_B200_PREFILL_BN = 128 | 192 | 256 forces a width (for tuning runs).
+    static int forced = -1;
+    if (forced < 0) {
+        const char *e = std::getenv("TESSL_B200_PREFILL_BN");
+        const int v = e ? std::atoi(e) : 0;
+        forced = (v == 128 || v == 192 || v == 256) ? v : 0;
+    }
+    if (forced) return forced;
     int best_bn = 256;
     uint64_t best_cost = ~0ull;
     for (int bn : {256, 192, 128}) {
         const uint64_t tiles = tiles_m * ((n + bn - 1) / bn);
         const uint64_t waves = (tiles + slots - 1) / slots;
-        const uint64_t cost = waves * (uint64_t)bn;
+        // a K block costs a fixed part (measured: about 320 columns' worth) plus a part proportional to the width
+        const uint64_t cost = waves * (uint64_t)(bn + 320);
         if (cost < best_cost) best_cost = cost, best_bn = bn;
     }
     return best_bn;

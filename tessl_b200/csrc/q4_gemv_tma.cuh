@@ -79,12 +79,17 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity)
     return ok != 0;
 }
 /// Bounded wait: false if the phase did not complete within ~2 s or another
-/// thread of the block already gave up.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag)
+/// thread of the block already gave up. With `backoff_ns` the thread sleeps
+/// between polls: every poll is a shared-memory request, and a few dozen warps
+/// polling back to back delay the requests of the one thread whose wait is on
+/// the critical path.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag,
+                                          uint32_t backoff_ns = 0)
 {
     if (mbar_try(bar, parity)) return true;
     const long long t0 = clock64();
     for (uint32_t i = 1;; ++i) {
+        if (backoff_ns) __nanosleep(backoff_ns);
         if (mbar_try(bar, parity)) return true;
         if ((i & 63u) == 0) {
             if (*abort_flag) return false;
