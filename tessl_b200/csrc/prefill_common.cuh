@@ -380,5 +380,37 @@ __device__ __forceinline__ void tcgen05_mma_f16_pair_lo(uint32_t tmem_d, uint32_
         : "memory");
 }
 
+// Warp-wide forms for an issuing warp that stays converged: all 32 lanes execute
+// the surrounding loop (so stage numbers and descriptors are warp-uniform values)
+// and one elected lane, always the same one, issues the instruction.
+__device__ __forceinline__ void tcgen05_mma_f16_pair_elect(uint32_t tmem_d, uint32_t adesc_lo, uint32_t bdesc_lo,
+                                                           uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile(
+        "{\n\t.reg .pred p, e;\n\t.reg .b64 da, db;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "mov.b64 da, {%1, %5};\n\tmov.b64 db, {%2, %5};\n\t"
+        "elect.sync _|e, 0xffffffff;\n\t"
+        "@e tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %3, p;\n\t}" ::"r"(tmem_d),
+        "r"(adesc_lo), "r"(bdesc_lo), "r"(idesc), "r"(accumulate), "r"(kUmmaDescHi)
+        : "memory");
+}
+__device__ __forceinline__ void tcgen05_commit_pair_elect(uint32_t bar)
+{
+    const uint16_t mask = 3;
+    asm volatile(
+        "{\n\t.reg .pred e;\n\telect.sync _|e, 0xffffffff;\n\t"
+        "@e tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;\n\t}" ::"r"(
+            bar),
+        "h"(mask)
+        : "memory");
+}
+__device__ __forceinline__ void tcgen05_commit_pair_local_elect(uint32_t bar)
+{
+    asm volatile(
+        "{\n\t.reg .pred e;\n\telect.sync _|e, 0xffffffff;\n\t"
+        "@e tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}" ::"r"(bar)
+        : "memory");
+}
+
 }  // namespace pf
 }  // namespace tessl

@@ -175,11 +175,13 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PairCfg<BN>::THREADS
         }
     } else if (warp == 1) {
         // ------------------------------------------------ MMA issuer (leader CTA) ---
-        // One thread, once per K block: wait for the stage, four MMAs, one commit. The
-        // loop is kept to a few dozen instructions (no division, descriptor low words
-        // advanced by constants) because whatever it spends between two blocks is time
-        // the tensor cores can run dry.
-        if (lane == 0 && rank == 0) {
+        // Once per K block: wait for the stage, four MMAs, one commit. The whole warp
+        // runs the loop converged and one elected lane issues the tcgen05
+        // instructions: stage numbers and descriptors are then warp-uniform values,
+        // which is what those instructions take, and the loop stays a few dozen
+        // instructions (no division either). Whatever it spends between two blocks is
+        // time the tensor cores can run dry.
+        if (rank == 0) {
             constexpr uint32_t idesc = (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)((2 * BM) >> 4) << 24);
             const uint32_t a_lo0 = umma_desc_lo(base + C::OFF_A), b_lo0 = umma_desc_lo(base + C::OFF_B);
             RingPos<C::SA> ring;
@@ -188,7 +190,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PairCfg<BN>::THREADS
             for (uint32_t t = cluster_id; t < ntiles && ok_; t += nclusters, ++it) {
                 const uint32_t buf = it & 1u;
                 if (!mbar_wait(acc_empty(buf), ((it >> 1) & 1u) ^ 1u, abortp)) {
-                    fail(3, it);
+                    if (lane == 0) fail(3, it);
                     break;
                 }
                 tcgen05_fence_after();
@@ -196,7 +198,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PairCfg<BN>::THREADS
                 const uint32_t d = tmem_base + buf * 256u;
                 for (uint32_t kb = 0; kb < nkb; ++kb) {
                     if (!mbar_wait(full(ring.stage), ring.phase, abortp)) {
-                        fail(4, kb);
+                        if (lane == 0) fail(4, kb);
                         ok_ = false;
                         break;
                     }
@@ -204,20 +206,21 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PairCfg<BN>::THREADS
                     tcgen05_fence_after();
                     const uint32_t a_lo = a_lo0 + ring.stage * (C::A_BYTES >> 4);
                     const uint32_t b_lo = b_lo0 + ring.stage * (C::B_BYTES >> 4);
-                    tcgen05_mma_f16_pair_lo(d, a_lo, b_lo, idesc, kb);  // the tile's first MMA overwrites
+                    tcgen05_mma_f16_pair_elect(d, a_lo, b_lo, idesc, kb);  // the tile's first MMA overwrites
 #pragma unroll
-                    for (uint32_t k4 = 1; k4 < 4; ++k4) tcgen05_mma_f16_pair_lo(d, a_lo + 2 * k4, b_lo + 2 * k4, idesc, 1u);
-                    tcgen05_commit_pair(empty(ring.stage));  // both CTAs' A and B stages are free once these MMAs have read them
+                    for (uint32_t k4 = 1; k4 < 4; ++k4) tcgen05_mma_f16_pair_elect(d, a_lo + 2 * k4, b_lo + 2 * k4, idesc, 1u);
+                    tcgen05_commit_pair_elect(empty(ring.stage));  // both CTAs' A and B stages are free once these MMAs have read them
                     ring.advance();
                     TSTAMP(2);  // issue MMAs and commit
                 }
-                if (ok_) tcgen05_commit_pair(acc_full(buf));
+                if (ok_) tcgen05_commit_pair_elect(acc_full(buf));
             }
             // Nothing may still be reading shared memory or writing TMEM when the pair winds down.
-            tcgen05_commit_pair_local(done_bar);
+            tcgen05_commit_pair_local_elect(done_bar);
             const long long t0 = clock64();
             while (!mbar_try(done_bar, 0u))
                 if (clock64() - t0 > 4000000000ll) break;
+            __syncwarp();
         }
     } else if (warp == 3) {
         // idle: keeps the epilogue warps on TMEM lane quarters warp & 3
