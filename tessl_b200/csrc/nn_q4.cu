@@ -9,6 +9,7 @@
 #include "q4_gemv_main.cuh"
 #include "q4_gemv_warp.cuh"
 #include "q4_gemv_tma.cuh"
+#include "q4_gemv_mma.cuh"
 
 #include <cstdlib>
 #include "runtime.h"
@@ -196,6 +197,99 @@ Result launch_tma(TesslRuntime *rt, const Q4GemvParams &p)
     return cuda_check(rt, e, "q4_gemv launch");
 }
 
+/// The tensor-core kernel (q4_gemv_mma.cuh): rows of 1024, 2048 or 4096 columns
+/// whose sixteenth holds whole quantization groups, scale/bias rows that a bulk
+/// copy can fetch. TESSL_B200_GEMV_MMA=0 turns it off (tuning runs).
+bool mma_enabled()
+{
+    static int on = -1;
+    if (on < 0) {
+        const char *e = std::getenv("TESSL_B200_GEMV_MMA");
+        on = (e && e[0] == '0') ? 0 : 1;
+    }
+    return on != 0;
+}
+
+bool mma_ok(const Q4GemvParams &p)
+{
+    if (!mma_enabled()) return false;
+    if (p.cols != 1024 && p.cols != 2048 && p.cols != 4096) return false;
+    if (p.group_shift < 5 || p.group_shift > 7) return false;
+    if (((p.cols / 16) >> p.group_shift) == 0) return false;
+    for (int s = 0; s < p.nseg; ++s) {
+        const Q4Seg &a = p.seg[s];
+        if (((uintptr_t)a.sb0 & 15u) || (a.sb1 && ((uintptr_t)a.sb1 & 15u))) return false;
+    }
+    return true;
+}
+
+template <int SW, int WPG, int NB, bool BATCH>
+Result launch_mma_one(TesslRuntime *rt, const Q4GemvParams &p, int m)
+{
+    auto kernel = q4m::q4_gemv_mma_kernel<SW, WPG, NB, BATCH>;
+    constexpr uint32_t RPB = 16 / NB;
+    q4m::Params mp{};
+    uint32_t rb = 0;
+    for (int s = 0; s < p.nseg; ++s) {
+        const Q4Seg &a = p.seg[s];
+        mp.seg[s] = q4m::Seg{a.packed0, a.sb0, a.packed1, a.sb1, a.out, a.resid, a.rows, rb};
+        rb += (a.rows + RPB - 1) / RPB;
+    }
+    if (rb == 0) return ok();
+    mp.nseg = p.nseg, mp.total_rb = rb;
+    mp.x = p.x, mp.m = (uint32_t)m, mp.cols = p.cols, mp.group_shift = p.group_shift;
+    mp.epi = p.epi, mp.out_bf16 = p.out_bf16;
+    mp.status = rt->status_dev;
+    const uint32_t gpr = p.cols >> p.group_shift;
+    const uint32_t part = BATCH ? q4m::kConsumers * 16 * 8 * 4 : q4m::kConsumers * 16 * 4;
+    const uint32_t stage_bytes = 16 * ((p.cols >> 1) + q4m::kRowPad) + 16 * gpr * 4 + part;
+    const uint32_t stages = std::min<uint32_t>(8u, (216u * 1024u) / (stage_bytes + 24));
+    mp.stages = stages;
+    const size_t smem = (size_t)stages * (stage_bytes + 24);
+    static size_t smem_set = 0;
+    if (smem > smem_set) {
+        TESSL_TRY(cuda_check(rt, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
+                             "q4_gemv_mma: shared memory opt-in"));
+        smem_set = smem;
+    }
+    const uint32_t grid = std::min<uint32_t>(rb, (uint32_t)rt->sm_count);
+    cudaLaunchConfig_t lc{};
+    lc.gridDim = dim3(grid), lc.blockDim = dim3(q4m::kThreads), lc.dynamicSmemBytes = smem;
+    lc.stream = rt->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    lc.attrs = attr, lc.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&lc, kernel, mp);
+    rt->dispatch_count += 1;
+    return cuda_check(rt, e, "q4_gemv launch");
+}
+
+template <int SW, int WPG>
+Result launch_mma_sw(TesslRuntime *rt, const Q4GemvParams &p, int m, int nb)
+{
+    if (nb == 2) return launch_mma_one<SW, WPG, 2, false>(rt, p, m);
+    if (m == 1) return launch_mma_one<SW, WPG, 1, false>(rt, p, m);
+    return launch_mma_one<SW, WPG, 1, true>(rt, p, m);
+}
+
+Result launch_mma(TesslRuntime *rt, const Q4GemvParams &p, int m, int nb)
+{
+    const int sw = (int)(p.cols / 512), wpg = 1 << (p.group_shift - 5);
+    if (sw == 8) {
+        if (wpg == 1) return launch_mma_sw<8, 1>(rt, p, m, nb);
+        if (wpg == 2) return launch_mma_sw<8, 2>(rt, p, m, nb);
+        return launch_mma_sw<8, 4>(rt, p, m, nb);
+    }
+    if (sw == 4) {
+        if (wpg == 1) return launch_mma_sw<4, 1>(rt, p, m, nb);
+        if (wpg == 2) return launch_mma_sw<4, 2>(rt, p, m, nb);
+        return launch_mma_sw<4, 4>(rt, p, m, nb);
+    }
+    if (wpg == 1) return launch_mma_sw<2, 1>(rt, p, m, nb);
+    return launch_mma_sw<2, 2>(rt, p, m, nb);
+}
+
 /// The staged kernel needs every bulk copy 16-byte aligned and sized.
 bool tma_ok(const Q4GemvParams &p)
 {
@@ -214,6 +308,7 @@ bool tma_ok(const Q4GemvParams &p)
 Result launch_q4_gemv(TesslRuntime *rt, Q4GemvParams p, int m, int nb)
 {
     const uint32_t nchunks = std::max<uint32_t>(1u, (p.cols + q4k::kChunk - 1) / q4k::kChunk);
+    if (m >= 1 && m <= 8 && (nb == 1 || m == 1) && mma_ok(p)) return launch_mma(rt, p, m, nb);
     if (m == 1 && nchunks <= 4 && tma_ok(p)) {
         if (nb == 1) {
             if (nchunks == 1) return launch_tma<1, 8, 1>(rt, p);

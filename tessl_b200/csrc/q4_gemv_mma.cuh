@@ -1,0 +1,400 @@
+// Q4 GEMV / small-batch GEMM (M <= 8, rows of 1024, 2048 or 4096 columns) with
+// the dot products on the tensor cores.
+//
+// Why: on the FMA pipe a weight costs one FMA plus 7/8 of a bit-manipulation
+// instruction plus overheads, about 2 issue slots; HBM3e delivers ~46 weights
+// per clock and SM, which would need ~90 of the SM's 128 slots per clock, and
+// the FMA-pipe kernels measured compute-bound at ~30 weights per clock (73% of
+// the memory roofline on a long stream). The nibble -> bf16 step already
+// produces exactly the register layout of an `mma.sync.m16n8k16` A fragment
+// (two bf16 values 128 + q per 32-bit word), so here one MMA replaces 256 FMAs:
+// 16 weight rows x 16 columns against the activations as the B operand, whose 8
+// columns are the up to 8 rows of the batch (for M = 1 all 8 hold the same
+// vector). That is ~1.4 issue slots per weight; the kernel is then bound by the
+// weight stream. The batch rides along for free, so M = 2..8 costs what M = 1
+// costs.
+//
+// Structure (one persistent block per SM, 18 warps):
+//   warp 16   producer: streams row blocks (16 rows of one bank, or 8 + 8 rows of
+//             a gate/up pair) through a ring of stages with plain `cp.async.bulk`
+//             copies, one per row (each issued by its own lane) so that the rows
+//             sit 32 bytes past a multiple of 128 apart (bank-conflict-free reads),
+//             plus the rows' scale/bias pairs. It never waits for the preceding
+//             kernel: weights are not written by it.
+//   warps 0-15 consumers: warp w owns columns [w K/16, (w+1) K/16) of every row.
+//             Its activations for that slice stay in registers as B fragments for
+//             the whole launch. Per stage it runs one MMA chain per quantization
+//             group (the chain starts from zero because each group has its own
+//             scale), folds `scale * (dot - 128 xsum) + bias * xsum` in f32 like
+//             the other GEMV kernels, and leaves its partial sums in shared memory.
+//   warp 17   reducer: adds the 16 partial sums of each output in warp order,
+//             applies the epilogue (residual, SiLU/GELU gate) and stores.
+// A row's summation order depends only on K and the group size, so fused
+// gate/up, K/V and Q/K/V launches give the same bits as separate launches.
+//
+// Every mbarrier wait is bounded (see q4_gemv_tma.cuh).
+#pragma once
+
+#include "q4_gemv_tma.cuh"
+
+namespace tessl {
+namespace q4m {
+
+using q4k::and_or;
+using q4k::bulk_g2s;
+using q4k::kMagic;
+using q4k::lds32;
+using q4k::mbar_arrive;
+using q4k::mbar_expect_tx;
+using q4k::mbar_init;
+using q4k::mbar_try;
+using q4k::mbar_wait;
+using q4k::smem_u32;
+
+constexpr int kConsumers = 16;
+constexpr int kThreads = (kConsumers + 2) * 32;
+constexpr uint32_t kRowPad = 32;  // bytes; row pitch = K / 2 + 32
+
+struct Seg {
+    const uint8_t *packed0;
+    const uint32_t *sb0;
+    const uint8_t *packed1;  // second bank of a gate/up launch
+    const uint32_t *sb1;
+    void *out;
+    const float *resid;
+    uint32_t rows;
+    uint32_t rb_begin;  // first row block of this bank within the launch
+};
+
+struct Params {
+    Seg seg[3];
+    int nseg;
+    uint32_t total_rb;
+    const uint16_t *x;  // bf16 [m, cols]
+    uint32_t m;
+    uint32_t cols;
+    uint32_t group_shift;
+    uint32_t stages;
+    int epi;
+    int out_bf16;
+    uint32_t *status;
+};
+
+__device__ __forceinline__ uint2 lds64(uint32_t addr)
+{
+    uint2 v;
+    asm volatile("ld.shared.v2.u32 {%0,%1}, [%2];" : "=r"(v.x), "=r"(v.y) : "r"(addr));
+    return v;
+}
+__device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                         uint32_t b1)
+{
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+/// SW: packed words a lane reads per row of its warp's slice (K / 512).
+/// WPG: words of one lane per quantization group (G / 32).
+/// NB: banks per row block (2 = gate/up: rows 0-7 of the MMA are gate rows, 8-15 the same rows of up).
+/// BATCH: the 8 MMA columns are distinct batch rows (M >= 2) instead of 8 copies of one vector.
+template <int SW, int WPG, int NB, bool BATCH>
+__global__ void __launch_bounds__(kThreads, 1) q4_gemv_mma_kernel(const Params p)
+{
+    asm volatile("griddepcontrol.launch_dependents;");
+    constexpr int NGS = SW / WPG;     // groups per slice
+    constexpr int RPB = 16 / NB;      // rows per bank and stage
+    constexpr int NQ = (NGS + 3) / 4;  // affine groups per lane when M = 1
+    static_assert(SW % WPG == 0 && NGS >= 1, "a warp's slice holds whole groups");
+    extern __shared__ __align__(128) uint8_t smem[];
+    __shared__ int abort_flag;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t K = p.cols, gpr = K >> p.group_shift;
+    const uint32_t row_bytes = K >> 1, pitch = row_bytes + kRowPad, sb_row_bytes = gpr * 4;
+    const uint32_t part_bytes = BATCH ? kConsumers * 16 * 8 * 4 : kConsumers * 16 * 4;
+    const uint32_t off_sb = 16 * pitch, off_part = off_sb + 16 * sb_row_bytes;
+    const uint32_t stage_bytes = off_part + part_bytes;
+    const uint32_t S = p.stages;
+    const uint32_t ring = smem_u32(smem);
+    const uint32_t bars = ring + S * stage_bytes;
+    auto full = [&](uint32_t s) { return bars + 8 * s; };
+    auto empty = [&](uint32_t s) { return bars + 8 * (S + s); };
+    auto done = [&](uint32_t s) { return bars + 8 * (2 * S + s); };
+
+    const uint32_t rb_lo = (uint32_t)((uint64_t)p.total_rb * blockIdx.x / gridDim.x);
+    const uint32_t rb_hi = (uint32_t)((uint64_t)p.total_rb * (blockIdx.x + 1) / gridDim.x);
+    const uint32_t n_local = rb_hi - rb_lo;
+
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        for (uint32_t s = 0; s < S; ++s) mbar_init(full(s), 1), mbar_init(empty(s), 1), mbar_init(done(s), kConsumers);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    volatile int *abortp = &abort_flag;
+    auto fail = [&](uint32_t role, uint32_t where) {
+        *abortp = 1;
+        *(volatile uint32_t *)p.status = (0x40u << 24) | (role << 20) | (where & 0xfffffu);
+    };
+    auto locate = [&](uint32_t rb, Seg &sg, uint32_t &row0) {
+        int s = 0;
+        if (p.nseg > 1 && rb >= p.seg[1].rb_begin) s = 1;
+        if (p.nseg > 2 && rb >= p.seg[2].rb_begin) s = 2;
+        sg = p.seg[s];
+        row0 = (rb - sg.rb_begin) * RPB;
+    };
+
+    if (warp == kConsumers) {
+        // ------------------------------------------------ producer ---
+        // The whole warp runs the loop; per stage lane 0 posts the byte count and each
+        // row's copy is issued by its own lane (issuing them all from one thread costs
+        // about as long as the copies take to arrive).
+        uint32_t s = 0, ph = 0, issued = 0;
+        for (uint32_t j = 0; j < n_local; ++j) {
+            if (!mbar_wait(empty(s), ph ^ 1u, abortp, 64)) {
+                if (lane == 0) fail(1, j);
+                break;
+            }
+            Seg sg;
+            uint32_t row0;
+            locate(rb_lo + j, sg, row0);
+            const uint32_t nrows = min((uint32_t)RPB, sg.rows - row0);
+            const uint32_t st = ring + s * stage_bytes;
+            if (lane == 0) mbar_expect_tx(full(s), NB * nrows * (row_bytes + sb_row_bytes));
+            __syncwarp();
+            if (lane < 16) {
+                const uint32_t b = (uint32_t)lane / RPB, r = (uint32_t)lane % RPB;
+                if (r < nrows) {
+                    const uint8_t *pk = (b == 0 ? sg.packed0 : sg.packed1) + (size_t)(row0 + r) * row_bytes;
+                    bulk_g2s(st + lane * pitch, pk, row_bytes, full(s));
+                }
+            } else if (lane < 16 + NB) {
+                const uint32_t b = (uint32_t)lane - 16;
+                const uint32_t *sb = (b == 0 ? sg.sb0 : sg.sb1) + (size_t)row0 * gpr;
+                bulk_g2s(st + off_sb + b * RPB * sb_row_bytes, sb, nrows * sb_row_bytes, full(s));
+            }
+            ++issued;
+            if (++s == S) s = 0, ph ^= 1u;
+        }
+        // After a timeout elsewhere copies may still be in flight: give the last ring a bounded chance to land.
+        if (*abortp && lane == 0) {
+            for (uint32_t i = issued > S ? issued - S : 0; i < issued; ++i) {
+                const long long t0 = clock64();
+                while (!mbar_try(full(i % S), (i / S) & 1u))
+                    if (clock64() - t0 > 4000000000ll) break;
+            }
+        }
+    } else if (warp == kConsumers + 1) {
+        // ------------------------------------------------ reducer ---
+        asm volatile("griddepcontrol.wait;" ::: "memory");  // y and resid belong to the stream's order
+        uint32_t s = 0, ph = 0;
+        for (uint32_t j = 0; j < n_local; ++j) {
+            if (!mbar_wait(done(s), ph, abortp, 32)) {
+                if (lane == 0) fail(3, j);
+                break;
+            }
+            Seg sg;
+            uint32_t row0;
+            locate(rb_lo + j, sg, row0);
+            const uint32_t part = ring + s * stage_bytes + off_part;
+            if constexpr (!BATCH) {
+                // lane r < RPB: output row row0 + r (for a gate/up pair also its up partner, MMA row r + 8)
+                if (lane < RPB && row0 + lane < sg.rows) {
+                    float v0 = 0.0f, v1 = 0.0f;
+#pragma unroll
+                    for (int w = 0; w < kConsumers; ++w) {
+                        v0 += __uint_as_float(lds32(part + (w * 16 + lane) * 4));
+                        if (NB == 2) v1 += __uint_as_float(lds32(part + (w * 16 + lane + 8) * 4));
+                    }
+                    const uint32_t row = row0 + lane;
+                    float v = v0;
+                    if (p.epi == q4k::EPI_ADD_RESID) {
+                        v = v + sg.resid[row];
+                    } else if (p.epi == q4k::EPI_GATE_UP_SILU) {
+                        v = dev::silu(v0) * v1;
+                    } else if (p.epi == q4k::EPI_GATE_UP_GELU) {
+                        v = dev::gelu_pytorch_tanh(v0) * v1;
+                    }
+                    if (p.out_bf16) {
+                        static_cast<uint16_t *>(sg.out)[row] = dev::f32_to_bf16_store(v);
+                    } else {
+                        static_cast<float *>(sg.out)[row] = v;
+                    }
+                }
+            } else {
+                // lane l: MMA row l / 2, batch columns 4 (l % 2) .. + 3
+                const uint32_t r = lane >> 1, c0 = (lane & 1) * 4;
+                float v[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+                for (int w = 0; w < kConsumers; ++w) {
+                    const uint4 q = q4k::lds128(part + ((w * 16 + r) * 8 + c0) * 4);
+                    v[0] += __uint_as_float(q.x), v[1] += __uint_as_float(q.y);
+                    v[2] += __uint_as_float(q.z), v[3] += __uint_as_float(q.w);
+                }
+                const uint32_t row = row0 + r;
+                if (row < sg.rows) {
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        const uint32_t n = c0 + c;
+                        if (n < p.m) {
+                            float o = v[c];
+                            const size_t idx = (size_t)n * sg.rows + row;
+                            if (p.epi == q4k::EPI_ADD_RESID) o = o + sg.resid[idx];
+                            if (p.out_bf16) {
+                                static_cast<uint16_t *>(sg.out)[idx] = dev::f32_to_bf16_store(o);
+                            } else {
+                                static_cast<float *>(sg.out)[idx] = o;
+                            }
+                        }
+                    }
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(empty(s));  // partial sums read: the stage may be refilled
+            if (++s == S) s = 0, ph ^= 1u;
+        }
+    } else {
+        // ------------------------------------------------ consumers ---
+        const uint32_t g = lane >> 2, t = lane & 3;
+        const uint32_t k0 = (uint32_t)warp * (K / kConsumers);  // first column of this warp's slice
+        const uint32_t G = 1u << p.group_shift;
+        // x is written by the preceding kernel in a decode chain: wait for it.
+        asm volatile("griddepcontrol.wait;" ::: "memory");
+        // B fragments of the slice: word (jj, u) of this lane covers columns
+        // k0 + jj G + t G / 4 + 8 u .. + 7, in the order 0,4,1,5,2,6,3,7 that the
+        // nibble-pair extraction below produces.
+        uint32_t xb[SW][4];
+        float xs[NGS];  // group sums of the activations: column g (BATCH) or the vector (M = 1)
+        {
+            const uint32_t n = BATCH ? min(g, p.m - 1) : 0u;
+            const uint16_t *xrow = p.x + (size_t)n * K;
+#pragma unroll
+            for (int jj = 0; jj < NGS; ++jj) {
+                float part = 0.0f;
+#pragma unroll
+                for (int u = 0; u < WPG; ++u) {
+                    const uint32_t k = k0 + jj * G + t * (G / 4) + 8 * u;
+                    const uint4 r = __ldg(reinterpret_cast<const uint4 *>(xrow + k));
+                    xb[jj * WPG + u][0] = __byte_perm(r.x, r.z, 0x5410);  // x0, x4
+                    xb[jj * WPG + u][1] = __byte_perm(r.x, r.z, 0x7632);  // x1, x5
+                    xb[jj * WPG + u][2] = __byte_perm(r.y, r.w, 0x5410);  // x2, x6
+                    xb[jj * WPG + u][3] = __byte_perm(r.y, r.w, 0x7632);  // x3, x7
+                    part += (dev::bf16_lo(r.x) + dev::bf16_hi(r.x)) + (dev::bf16_lo(r.y) + dev::bf16_hi(r.y));
+                    part += (dev::bf16_lo(r.z) + dev::bf16_hi(r.z)) + (dev::bf16_lo(r.w) + dev::bf16_hi(r.w));
+                }
+                part += __shfl_xor_sync(0xffffffffu, part, 1);
+                part += __shfl_xor_sync(0xffffffffu, part, 2);
+                xs[jj] = part;  // the same in the four lanes of a quad
+            }
+        }
+        // BATCH: this lane's outputs are batch columns 2 t and 2 t + 1; their group sums live in quads 2 t and 2 t + 1.
+        float xs0[BATCH ? NGS : 1], xs1[BATCH ? NGS : 1];
+        if constexpr (BATCH) {
+#pragma unroll
+            for (int jj = 0; jj < NGS; ++jj) {
+                xs0[jj] = __shfl_sync(0xffffffffu, xs[jj], (2 * t) * 4);
+                xs1[jj] = __shfl_sync(0xffffffffu, xs[jj], (2 * t + 1) * 4);
+            }
+        }
+        const uint32_t w_off = (k0 >> 1) + t * (G / 8);  // byte offset of the lane's first word within a row
+        const uint32_t sb_off = (k0 >> p.group_shift) * 4;
+
+        uint32_t s = 0, ph = 0;
+        for (uint32_t j = 0; j < n_local; ++j) {
+            if (!mbar_wait(full(s), ph, abortp)) {
+                if (lane == 0) fail(2, j);
+                break;
+            }
+            const uint32_t st = ring + s * stage_bytes;
+            const uint32_t row_lo = st + g * pitch + w_off, row_hi = row_lo + 8 * pitch;
+            const uint32_t sb_lo = st + off_sb + g * sb_row_bytes + sb_off, sb_hi = sb_lo + 8 * sb_row_bytes;
+            float dlo[NGS], dhi[NGS];        // M = 1: dot of MMA rows g and g + 8 per group
+            // BATCH: rows g, g + 8 x columns 2 t, 2 t + 1, one accumulator per group class jj % 4 so that
+            // the sum is formed in the same order as in the M = 1 path (where lane t of a quad takes
+            // the groups t, t + 4, ... and the quad is then added up by a butterfly)
+            float acc[4][4] = {};
+#pragma unroll
+            for (int jj = 0; jj < NGS; ++jj) {
+                float d[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+                for (int u2 = 0; u2 < WPG; u2 += 2) {
+                    // one or two words of each of the two rows
+                    uint32_t wl[2], wh[2];
+                    if constexpr (WPG >= 2) {
+                        const uint2 a = lds64(row_lo + jj * (G / 2) + 4 * u2), b = lds64(row_hi + jj * (G / 2) + 4 * u2);
+                        wl[0] = a.x, wl[1] = a.y, wh[0] = b.x, wh[1] = b.y;
+                    } else {
+                        wl[0] = lds32(row_lo + jj * (G / 2)), wh[0] = lds32(row_hi + jj * (G / 2));
+                        wl[1] = wh[1] = 0;
+                    }
+#pragma unroll
+                    for (int uu = 0; uu < (WPG >= 2 ? 2 : 1); ++uu) {
+                        const uint32_t a = wl[uu], b = wh[uu];
+                        const uint32_t (&xf)[4] = xb[jj * WPG + u2 + uu];
+                        // nibble pairs (i, i + 4) as two bf16 values 128 + q: exactly an A-fragment register
+                        const uint32_t a0 = and_or(a, 0x000f000fu, kMagic), b0 = and_or(b, 0x000f000fu, kMagic);
+                        // (the shifts share the LOP3s' pipe, this kernel's busiest; `mul.hi` by 2^28 on the
+                        // multiply pipe instead measured 40% slower)
+                        const uint32_t a1 = and_or(a >> 4, 0x000f000fu, kMagic), b1 = and_or(b >> 4, 0x000f000fu, kMagic);
+                        const uint32_t a2 = and_or(a >> 8, 0x000f000fu, kMagic), b2 = and_or(b >> 8, 0x000f000fu, kMagic);
+                        const uint32_t a3 = and_or(a >> 12, 0x000f000fu, kMagic), b3 = and_or(b >> 12, 0x000f000fu, kMagic);
+                        mma_bf16(d, a0, b0, a1, b1, xf[0], xf[1]);  // columns 0,4 | 1,5 of the word
+                        mma_bf16(d, a2, b2, a3, b3, xf[2], xf[3]);  // columns 2,6 | 3,7
+                    }
+                }
+                if constexpr (BATCH) {
+                    const uint32_t pl = lds32(sb_lo + jj * 4), ph2 = lds32(sb_hi + jj * 4);
+                    const float sl = dev::bf16_lo(pl), bl = dev::bf16_hi(pl), sh = dev::bf16_lo(ph2), bh = dev::bf16_hi(ph2);
+                    const int cls = jj & 3;  // a constant once the loop is unrolled
+                    acc[0][cls] = fmaf(sl, fmaf(-128.0f, xs0[jj], d[0]), fmaf(bl, xs0[jj], acc[0][cls]));
+                    acc[1][cls] = fmaf(sl, fmaf(-128.0f, xs1[jj], d[1]), fmaf(bl, xs1[jj], acc[1][cls]));
+                    acc[2][cls] = fmaf(sh, fmaf(-128.0f, xs0[jj], d[2]), fmaf(bh, xs0[jj], acc[2][cls]));
+                    acc[3][cls] = fmaf(sh, fmaf(-128.0f, xs1[jj], d[3]), fmaf(bh, xs1[jj], acc[3][cls]));
+                } else {
+                    dlo[jj] = d[0], dhi[jj] = d[2];  // every column holds the same vector: d[1] == d[0]
+                }
+            }
+            const uint32_t part = st + off_part;
+            if constexpr (BATCH) {
+                float o[4];
+#pragma unroll
+                for (int c = 0; c < 4; ++c) o[c] = (acc[c][0] + acc[c][1]) + (acc[c][2] + acc[c][3]);
+                asm volatile("st.shared.v2.f32 [%0], {%1,%2};" ::"r"(part + ((warp * 16 + g) * 8 + 2 * t) * 4), "f"(o[0]),
+                             "f"(o[1])
+                             : "memory");
+                asm volatile("st.shared.v2.f32 [%0], {%1,%2};" ::"r"(part + ((warp * 16 + g + 8) * 8 + 2 * t) * 4),
+                             "f"(o[2]), "f"(o[3])
+                             : "memory");
+            } else {
+                // The four lanes of a quad hold the same dots: lane t folds the affine of groups t, t + 4, ...
+                float vlo = 0.0f, vhi = 0.0f;
+#pragma unroll
+                for (int q = 0; q < NQ; ++q) {
+                    float dl = 0.0f, dh = 0.0f, xg = 0.0f;
+#pragma unroll
+                    for (int i = 0; i < 4; ++i)
+                        if (4 * q + i < NGS && t == (uint32_t)i) dl = dlo[4 * q + i], dh = dhi[4 * q + i], xg = xs[4 * q + i];
+                    const uint32_t jj = 4 * q + t;
+                    if (jj < (uint32_t)NGS) {
+                        const uint32_t pl = lds32(sb_lo + jj * 4), ph2 = lds32(sb_hi + jj * 4);
+                        vlo = fmaf(dev::bf16_lo(pl), fmaf(-128.0f, xg, dl), fmaf(dev::bf16_hi(pl), xg, vlo));
+                        vhi = fmaf(dev::bf16_lo(ph2), fmaf(-128.0f, xg, dh), fmaf(dev::bf16_hi(ph2), xg, vhi));
+                    }
+                }
+                vlo += __shfl_xor_sync(0xffffffffu, vlo, 1), vhi += __shfl_xor_sync(0xffffffffu, vhi, 1);
+                vlo += __shfl_xor_sync(0xffffffffu, vlo, 2), vhi += __shfl_xor_sync(0xffffffffu, vhi, 2);
+                if (t == 0) {
+                    asm volatile("st.shared.f32 [%0], %1;" ::"r"(part + (warp * 16 + g) * 4), "f"(vlo) : "memory");
+                    asm volatile("st.shared.f32 [%0], %1;" ::"r"(part + (warp * 16 + g + 8) * 4), "f"(vhi) : "memory");
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(done(s));  // release: the partial sums are visible to the reducer
+            if (++s == S) s = 0, ph ^= 1u;
+        }
+    }
+}
+
+}  // namespace q4m
+}  // namespace tessl

@@ -166,6 +166,51 @@ def test_small_m_gemm_matches_the_oracle(rt, rows, cols, group, m):
     assert np.array_equal(r.read(np.float32, m * rows), got.reshape(-1) + resid)
 
 
+TENSOR_GEMV_SHAPES = [(40, 1024, 32), (257, 1024, 64), (40, 2048, 32), (257, 2048, 64), (72, 2048, 128),
+                      (40, 4096, 32), (129, 4096, 64), (257, 4096, 128)]
+
+
+@pytest.mark.parametrize("rows,cols,group", TENSOR_GEMV_SHAPES)
+def test_tensor_core_gemv_shapes(rt, rows, cols, group):
+    """Rows of 1024, 2048 or 4096 columns run on the MMA kernel: every (K, G) it is built
+    for, ragged row counts, batches of 1, 3 and 8, and the fused gate/up launch against
+    two plain launches."""
+    packed, sb, _ = make_case(rows, cols, group, 0x7E550090 + rows + cols)
+    bank = upload_bank(rt, packed, sb)
+    shape = nn.QuantShape(rows, cols, group)
+    for m in (1, 3, 8):
+        x = synth.normal_bf16(0x7E550097 + m + cols, m * cols)
+        xb = rt.buffer_from(x)
+        y = seeded_f32(rt, m * rows, 8)
+        if m == 1:
+            nn.gemv_q4_mlx_simd(rt, bank, xb, y, shape)
+        else:
+            nn.gemm_q4_mlx(rt, bank, xb, y, shape, m)
+        got = y.read(np.float32, m * rows + 8)
+        assert np.all(got[m * rows:] == SENTINEL_F32), f"wrote past y (m={m})"
+        got = got[: m * rows].reshape(m, rows)
+        want = api.q4_dense_gemm(packed, sb, x, m, rows, cols, group)
+        assert_north_star(got, want, f"tensor-core gemv m={m} {rows}x{cols} g{group}")
+        assert_gamma_bound(got, packed, sb, x, m, rows, cols, group, what=f"tensor-core gemv m={m}")
+        if m > 1:  # a batch row equals the same vector run alone, bit for bit
+            x0 = rt.buffer_from(x[:cols].copy())
+            y0 = seeded_f32(rt, rows)
+            nn.gemv_q4_mlx_simd(rt, bank, x0, y0, shape)
+            assert np.array_equal(y0.read(np.float32, rows), got[0])
+    up, us, x = make_case(rows, cols, group, 0x7E5500A0 + rows + cols)
+    upb, xb = upload_bank(rt, up, us), rt.buffer_from(x)
+    mid = rt.buffer_from(np.full((rows + 8) * 4, 0xA5, np.uint8))
+    nn.gemv_q4_mlx_gate_up_silu(rt, bank, upb, xb, mid, shape, False)
+    fused = mid.read(np.uint8, (rows + 8) * 4)
+    assert np.all(fused[rows * 4:] == 0xA5), "wrote past mid"
+    g, u = seeded_f32(rt, rows), seeded_f32(rt, rows)
+    nn.gemv_q4_mlx_simd(rt, bank, xb, g, shape)
+    nn.gemv_q4_mlx_simd(rt, upb, xb, u, shape)
+    out = seeded_f32(rt, rows)
+    nn.swiglu(rt, g, u, out, rows, False)
+    assert np.array_equal(fused[: rows * 4], out.read(np.uint8, rows * 4))
+
+
 def test_refusals_happen_before_any_launch(rt):
     rows, cols, group = 40, 256, 64
     packed, sb, x = make_case(rows, cols, group, 1)
