@@ -51,6 +51,11 @@ using q4k::mbar_try;
 using q4k::mbar_wait;
 using q4k::smem_u32;
 
+// Blocks per SM the register budget is compiled for (2 lets the next launch's block start
+// beside this one's when the ring is short enough).
+#ifndef TESSL_GEMV_MMA_MIN_BLOCKS
+#define TESSL_GEMV_MMA_MIN_BLOCKS 1
+#endif
 constexpr int kConsumers = 16;
 constexpr int kThreads = (kConsumers + 2) * 32;
 constexpr uint32_t kRowPad = 32;  // bytes; row pitch = K / 2 + 32
@@ -78,7 +83,23 @@ struct Params {
     int epi;
     int out_bf16;
     uint32_t *status;
+#ifdef TESSL_GEMV_TIMING
+    unsigned long long *timing;  // [grid][8] cycles per role and phase (development builds only)
+#endif
 };
+
+#ifdef TESSL_GEMV_TIMING
+#define MMA_TSTAMP(i)                      \
+    do {                                   \
+        const long long _now = clock64();  \
+        tacc[i] += _now - tlast;           \
+        tlast = _now;                      \
+    } while (0)
+#else
+#define MMA_TSTAMP(i) \
+    do {              \
+    } while (0)
+#endif
 
 __device__ __forceinline__ uint2 lds64(uint32_t addr)
 {
@@ -89,8 +110,7 @@ __device__ __forceinline__ uint2 lds64(uint32_t addr)
 __device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
                                          uint32_t b1)
 {
-    asm volatile(
-        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
         : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
@@ -100,7 +120,7 @@ __device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1
 /// NB: banks per row block (2 = gate/up: rows 0-7 of the MMA are gate rows, 8-15 the same rows of up).
 /// BATCH: the 8 MMA columns are distinct batch rows (M >= 2) instead of 8 copies of one vector.
 template <int SW, int WPG, int NB, bool BATCH>
-__global__ void __launch_bounds__(kThreads, 1) q4_gemv_mma_kernel(const Params p)
+__global__ void __launch_bounds__(kThreads, TESSL_GEMV_MMA_MIN_BLOCKS) q4_gemv_mma_kernel(const Params p)
 {
     asm volatile("griddepcontrol.launch_dependents;");
     constexpr int NGS = SW / WPG;     // groups per slice
@@ -137,6 +157,11 @@ __global__ void __launch_bounds__(kThreads, 1) q4_gemv_mma_kernel(const Params p
         *abortp = 1;
         *(volatile uint32_t *)p.status = (0x40u << 24) | (role << 20) | (where & 0xfffffu);
     };
+#ifdef TESSL_GEMV_TIMING
+    long long tacc[2] = {0, 0};
+    const long long tstart = clock64();
+    long long tlast = tstart;
+#endif
     auto locate = [&](uint32_t rb, Seg &sg, uint32_t &row0) {
         int s = 0;
         if (p.nseg > 1 && rb >= p.seg[1].rb_begin) s = 1;
@@ -149,33 +174,59 @@ __global__ void __launch_bounds__(kThreads, 1) q4_gemv_mma_kernel(const Params p
         // ------------------------------------------------ producer ---
         // The whole warp runs the loop; per stage lane 0 posts the byte count and each
         // row's copy is issued by its own lane (issuing them all from one thread costs
-        // about as long as the copies take to arrive).
+        // about as long as the copies take to arrive). The loop is kept to a handful of
+        // instructions per stage: the warp shares its scheduler with consumer warps that
+        // saturate it, so every instruction here waits for an issue slot. Lanes 0-15 own
+        // the 16 row slots of a stage, lanes 16 (and 17) the scale/bias rows of a bank.
+        const uint32_t my_bank = lane < 16 ? (uint32_t)lane / RPB : (uint32_t)lane - 16;
+        const uint32_t my_r = lane < 16 ? (uint32_t)lane % RPB : 0u;
+        const bool copies = lane < 16 + NB;
+        const uint32_t my_dst = lane < 16 ? (uint32_t)lane * pitch : off_sb + my_bank * RPB * sb_row_bytes;
         uint32_t s = 0, ph = 0, issued = 0;
+        int cur_seg = -1;
+        uint32_t seg_end_rb = 0, seg_rows = 0, row0 = 0;
+        const uint8_t *src = nullptr;   // this lane's next source: a packed row (lanes 0-15) or the block's scale rows
+        uint32_t src_step = 0;
         for (uint32_t j = 0; j < n_local; ++j) {
+            const uint32_t rb = rb_lo + j;
+            if (cur_seg < 0 || rb >= seg_end_rb) {
+                // entering a bank: this lane's source pointer and stride within it
+                int sidx = 0;
+                if (p.nseg > 1 && rb >= p.seg[1].rb_begin) sidx = 1;
+                if (p.nseg > 2 && rb >= p.seg[2].rb_begin) sidx = 2;
+                cur_seg = sidx;
+                const Seg &sg = p.seg[sidx];
+                seg_rows = sg.rows;
+                seg_end_rb = sg.rb_begin + (sg.rows + RPB - 1) / RPB;
+                row0 = (rb - sg.rb_begin) * RPB;
+                if (lane < 16) {
+                    src = (my_bank == 0 ? sg.packed0 : sg.packed1) + (size_t)(row0 + my_r) * row_bytes;
+                    src_step = RPB * row_bytes;
+                } else {
+                    src = reinterpret_cast<const uint8_t *>((my_bank == 0 ? sg.sb0 : sg.sb1)) + (size_t)row0 * sb_row_bytes;
+                    src_step = RPB * sb_row_bytes;
+                }
+            }
             if (!mbar_wait(empty(s), ph ^ 1u, abortp, 64)) {
                 if (lane == 0) fail(1, j);
                 break;
             }
-            Seg sg;
-            uint32_t row0;
-            locate(rb_lo + j, sg, row0);
-            const uint32_t nrows = min((uint32_t)RPB, sg.rows - row0);
+            MMA_TSTAMP(0);  // wait empty
+            const uint32_t nrows = min((uint32_t)RPB, seg_rows - row0);
             const uint32_t st = ring + s * stage_bytes;
             if (lane == 0) mbar_expect_tx(full(s), NB * nrows * (row_bytes + sb_row_bytes));
             __syncwarp();
-            if (lane < 16) {
-                const uint32_t b = (uint32_t)lane / RPB, r = (uint32_t)lane % RPB;
-                if (r < nrows) {
-                    const uint8_t *pk = (b == 0 ? sg.packed0 : sg.packed1) + (size_t)(row0 + r) * row_bytes;
-                    bulk_g2s(st + lane * pitch, pk, row_bytes, full(s));
+            if (copies) {
+                if (lane >= 16) {
+                    bulk_g2s(st + my_dst, src, nrows * sb_row_bytes, full(s));
+                } else if (my_r < nrows) {
+                    bulk_g2s(st + my_dst, src, row_bytes, full(s));
                 }
-            } else if (lane < 16 + NB) {
-                const uint32_t b = (uint32_t)lane - 16;
-                const uint32_t *sb = (b == 0 ? sg.sb0 : sg.sb1) + (size_t)row0 * gpr;
-                bulk_g2s(st + off_sb + b * RPB * sb_row_bytes, sb, nrows * sb_row_bytes, full(s));
             }
+            src += src_step, row0 += RPB;
             ++issued;
             if (++s == S) s = 0, ph ^= 1u;
+            MMA_TSTAMP(1);  // issue
         }
         // After a timeout elsewhere copies may still be in flight: give the last ring a bounded chance to land.
         if (*abortp && lane == 0) {
@@ -194,6 +245,7 @@ __global__ void __launch_bounds__(kThreads, 1) q4_gemv_mma_kernel(const Params p
                 if (lane == 0) fail(3, j);
                 break;
             }
+            MMA_TSTAMP(0);  // wait done
             Seg sg;
             uint32_t row0;
             locate(rb_lo + j, sg, row0);
@@ -253,6 +305,7 @@ __global__ void __launch_bounds__(kThreads, 1) q4_gemv_mma_kernel(const Params p
             __syncwarp();
             if (lane == 0) mbar_arrive(empty(s));  // partial sums read: the stage may be refilled
             if (++s == S) s = 0, ph ^= 1u;
+            MMA_TSTAMP(1);  // reduce and store
         }
     } else {
         // ------------------------------------------------ consumers ---
@@ -301,11 +354,16 @@ __global__ void __launch_bounds__(kThreads, 1) q4_gemv_mma_kernel(const Params p
         const uint32_t sb_off = (k0 >> p.group_shift) * 4;
 
         uint32_t s = 0, ph = 0;
+#ifdef TESSL_GEMV_TIMING
+        const long long tsetup = clock64() - tstart;
+        tlast = clock64();
+#endif
         for (uint32_t j = 0; j < n_local; ++j) {
-            if (!mbar_wait(full(s), ph, abortp)) {
+            if (!mbar_wait(full(s), ph, abortp, 32)) {  // sleeping between polls leaves issue slots to the producer
                 if (lane == 0) fail(2, j);
                 break;
             }
+            MMA_TSTAMP(0);  // wait full
             const uint32_t st = ring + s * stage_bytes;
             const uint32_t row_lo = st + g * pitch + w_off, row_hi = row_lo + 8 * pitch;
             const uint32_t sb_lo = st + off_sb + g * sb_row_bytes + sb_off, sb_hi = sb_lo + 8 * sb_row_bytes;
@@ -314,45 +372,57 @@ __global__ void __launch_bounds__(kThreads, 1) q4_gemv_mma_kernel(const Params p
             // the sum is formed in the same order as in the M = 1 path (where lane t of a quad takes
             // the groups t, t + 4, ... and the quad is then added up by a butterfly)
             float acc[4][4] = {};
+            // All words of the slice first (the rows were copied long ago: these loads do not wait),
+            // then the MMAs interleaved over the groups: consecutive MMAs belong to different
+            // accumulator chains, so none waits for its predecessor. Within a chain the order is
+            // word by word, first half before second, whatever the interleaving.
+            uint32_t wl[SW], wh[SW];
 #pragma unroll
             for (int jj = 0; jj < NGS; ++jj) {
-                float d[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                if constexpr (WPG >= 2) {
 #pragma unroll
-                for (int u2 = 0; u2 < WPG; u2 += 2) {
-                    // one or two words of each of the two rows
-                    uint32_t wl[2], wh[2];
-                    if constexpr (WPG >= 2) {
+                    for (int u2 = 0; u2 < WPG; u2 += 2) {
                         const uint2 a = lds64(row_lo + jj * (G / 2) + 4 * u2), b = lds64(row_hi + jj * (G / 2) + 4 * u2);
-                        wl[0] = a.x, wl[1] = a.y, wh[0] = b.x, wh[1] = b.y;
-                    } else {
-                        wl[0] = lds32(row_lo + jj * (G / 2)), wh[0] = lds32(row_hi + jj * (G / 2));
-                        wl[1] = wh[1] = 0;
+                        wl[jj * WPG + u2] = a.x, wl[jj * WPG + u2 + 1] = a.y;
+                        wh[jj * WPG + u2] = b.x, wh[jj * WPG + u2 + 1] = b.y;
                     }
-#pragma unroll
-                    for (int uu = 0; uu < (WPG >= 2 ? 2 : 1); ++uu) {
-                        const uint32_t a = wl[uu], b = wh[uu];
-                        const uint32_t (&xf)[4] = xb[jj * WPG + u2 + uu];
-                        // nibble pairs (i, i + 4) as two bf16 values 128 + q: exactly an A-fragment register
-                        const uint32_t a0 = and_or(a, 0x000f000fu, kMagic), b0 = and_or(b, 0x000f000fu, kMagic);
-                        // (the shifts share the LOP3s' pipe, this kernel's busiest; `mul.hi` by 2^28 on the
-                        // multiply pipe instead measured 40% slower)
-                        const uint32_t a1 = and_or(a >> 4, 0x000f000fu, kMagic), b1 = and_or(b >> 4, 0x000f000fu, kMagic);
-                        const uint32_t a2 = and_or(a >> 8, 0x000f000fu, kMagic), b2 = and_or(b >> 8, 0x000f000fu, kMagic);
-                        const uint32_t a3 = and_or(a >> 12, 0x000f000fu, kMagic), b3 = and_or(b >> 12, 0x000f000fu, kMagic);
-                        mma_bf16(d, a0, b0, a1, b1, xf[0], xf[1]);  // columns 0,4 | 1,5 of the word
-                        mma_bf16(d, a2, b2, a3, b3, xf[2], xf[3]);  // columns 2,6 | 3,7
-                    }
+                } else {
+                    wl[jj] = lds32(row_lo + jj * (G / 2)), wh[jj] = lds32(row_hi + jj * (G / 2));
                 }
+            }
+            float d[NGS][4] = {};
+#pragma unroll
+            for (int u = 0; u < WPG; ++u) {
+#pragma unroll
+                for (int jj = 0; jj < NGS; ++jj) {
+                    const uint32_t a = wl[jj * WPG + u], b = wh[jj * WPG + u];
+                    // nibble pairs (i, i + 4) as two bf16 values 128 + q: exactly an A-fragment register
+                    // (the shifts share the LOP3s' pipe, this kernel's busiest; `mul.hi` by 2^28 on the
+                    // multiply pipe instead measured 40% slower)
+                    const uint32_t a0 = and_or(a, 0x000f000fu, kMagic), b0 = and_or(b, 0x000f000fu, kMagic);
+                    const uint32_t a1 = and_or(a >> 4, 0x000f000fu, kMagic), b1 = and_or(b >> 4, 0x000f000fu, kMagic);
+                    mma_bf16(d[jj], a0, b0, a1, b1, xb[jj * WPG + u][0], xb[jj * WPG + u][1]);  // columns 0,4 | 1,5
+                }
+#pragma unroll
+                for (int jj = 0; jj < NGS; ++jj) {
+                    const uint32_t a = wl[jj * WPG + u], b = wh[jj * WPG + u];
+                    const uint32_t a2 = and_or(a >> 8, 0x000f000fu, kMagic), b2 = and_or(b >> 8, 0x000f000fu, kMagic);
+                    const uint32_t a3 = and_or(a >> 12, 0x000f000fu, kMagic), b3 = and_or(b >> 12, 0x000f000fu, kMagic);
+                    mma_bf16(d[jj], a2, b2, a3, b3, xb[jj * WPG + u][2], xb[jj * WPG + u][3]);  // columns 2,6 | 3,7
+                }
+            }
+#pragma unroll
+            for (int jj = 0; jj < NGS; ++jj) {
                 if constexpr (BATCH) {
                     const uint32_t pl = lds32(sb_lo + jj * 4), ph2 = lds32(sb_hi + jj * 4);
                     const float sl = dev::bf16_lo(pl), bl = dev::bf16_hi(pl), sh = dev::bf16_lo(ph2), bh = dev::bf16_hi(ph2);
                     const int cls = jj & 3;  // a constant once the loop is unrolled
-                    acc[0][cls] = fmaf(sl, fmaf(-128.0f, xs0[jj], d[0]), fmaf(bl, xs0[jj], acc[0][cls]));
-                    acc[1][cls] = fmaf(sl, fmaf(-128.0f, xs1[jj], d[1]), fmaf(bl, xs1[jj], acc[1][cls]));
-                    acc[2][cls] = fmaf(sh, fmaf(-128.0f, xs0[jj], d[2]), fmaf(bh, xs0[jj], acc[2][cls]));
-                    acc[3][cls] = fmaf(sh, fmaf(-128.0f, xs1[jj], d[3]), fmaf(bh, xs1[jj], acc[3][cls]));
+                    acc[0][cls] = fmaf(sl, fmaf(-128.0f, xs0[jj], d[jj][0]), fmaf(bl, xs0[jj], acc[0][cls]));
+                    acc[1][cls] = fmaf(sl, fmaf(-128.0f, xs1[jj], d[jj][1]), fmaf(bl, xs1[jj], acc[1][cls]));
+                    acc[2][cls] = fmaf(sh, fmaf(-128.0f, xs0[jj], d[jj][2]), fmaf(bh, xs0[jj], acc[2][cls]));
+                    acc[3][cls] = fmaf(sh, fmaf(-128.0f, xs1[jj], d[jj][3]), fmaf(bh, xs1[jj], acc[3][cls]));
                 } else {
-                    dlo[jj] = d[0], dhi[jj] = d[2];  // every column holds the same vector: d[1] == d[0]
+                    dlo[jj] = d[jj][0], dhi[jj] = d[jj][2];  // every column holds the same vector: d[1] == d[0]
                 }
             }
             const uint32_t part = st + off_part;
@@ -392,8 +462,21 @@ __global__ void __launch_bounds__(kThreads, 1) q4_gemv_mma_kernel(const Params p
             __syncwarp();
             if (lane == 0) mbar_arrive(done(s));  // release: the partial sums are visible to the reducer
             if (++s == S) s = 0, ph ^= 1u;
+            MMA_TSTAMP(1);  // compute
         }
+#ifdef TESSL_GEMV_TIMING
+        if (p.timing && warp == 0 && lane == 0) p.timing[blockIdx.x * 16 + 6] = tsetup;
+#endif
     }
+#ifdef TESSL_GEMV_TIMING
+    if (p.timing && lane == 0 && (warp == 0 || warp >= kConsumers)) {
+        // rows of 2: consumer warp 0, producer, reducer; [6] consumer setup, [7] block total
+        const int role = warp == 0 ? 0 : warp == kConsumers ? 1 : 2;
+        unsigned long long *o = p.timing + blockIdx.x * 16;
+        o[2 * role] = tacc[0], o[2 * role + 1] = tacc[1];
+        if (warp == kConsumers + 1) o[7] = clock64() - tstart;
+    }
+#endif
 }
 
 }  // namespace q4m
