@@ -581,11 +581,11 @@ def main():
         dom_us = sum(pk[k]["us"] for k in dom)
         achieved = dom_bytes / dom_us / 1e3
         line["roofline"] = {
-            "bound": "hbm", "kernel": "q4_gemv_tma_kernel", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"],
+            "bound": "hbm", "kernel": "q4_gemv_mma_kernel", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"],
             "unit": "GB/s", "frac": round(achieved / peaks["hbm_gbs"], 4), "peak_source": peaks["source"],
             # ncu: dram__bytes_read+write of one 12288x4096 launch was 28.35 MB for 28.31 MB algorithmic
-            # (profiles/q4_gemv_12288x4096.md): traffic = algorithmic bytes x 1.0015 per launch.
-            "traffic": round(dom_bytes / 3 * 1.0015), "algorithmic_bytes_per_launch": dom_bytes // 3,
+            # (profiles/q4_gemv_mma_12288x4096.md): traffic = algorithmic bytes x 1.0013 per launch.
+            "traffic": round(dom_bytes / 3 * 1.0013), "algorithmic_bytes_per_launch": dom_bytes // 3,
             "launches_per_step": 3,
         }
         line["per_kernel"] = pk
