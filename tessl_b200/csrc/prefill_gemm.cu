@@ -506,6 +506,12 @@ Result prefill_validate(const TesslQ4MlxBank &bank, const TesslBuf &x_bf16, cons
     return ok();
 }
 
+/// The pair kernel's 256-row tile is half padding for m <= 128, but each CTA still expands only half of
+/// the weight rows and it has the better pipeline: measured 34.6 us against the single-CTA kernel's 48.9 us
+/// at m = 16 .. 64, N = 12288, K = 4096. So the pair kernel runs for every m; the single-CTA kernel is
+/// what TESSL_B200_PREFILL_PAIR=0 (or a GPU with one SM) selects.
+constexpr uint32_t kPairMinRows = 1;
+
 /// Tile width with the least estimated time: waves of tiles x the cost of one tile's K block.
 int pick_tile_width(uint64_t tiles_m, uint32_t n, uint32_t slots)
 {
@@ -529,16 +535,17 @@ int pick_tile_width(uint64_t tiles_m, uint32_t n, uint32_t slots)
     return best_bn;
 }
 
-/// 0 = single-CTA kernel only, 1 = CTA-pair kernel whenever there are at least two
-/// 128-row blocks (the default), from TESSL_B200_PREFILL_PAIR.
-int pair_mode()
+/// Rows of X from which the CTA-pair kernel is used: TESSL_B200_PREFILL_PAIR = 0 never,
+/// = n > 0 for m >= n; default below.
+uint32_t pair_min_rows()
 {
-    static int mode = -1;
-    if (mode < 0) {
+    static int64_t v = -1;
+    if (v < 0) {
         const char *e = std::getenv("TESSL_B200_PREFILL_PAIR");
-        mode = (e && e[0] == '0') ? 0 : 1;
+        v = e ? std::atoll(e) : (int64_t)kPairMinRows;
+        if (e && v <= 0) v = 0xffffffffll;
     }
-    return mode;
+    return (uint32_t)v;
 }
 
 /// Pre-pass and GEMM of a validated call; `scratch` holds `plan.need` bytes.
@@ -552,7 +559,7 @@ Result prefill_launch(TesslRuntime *rt, const TesslQ4MlxBank &bank, const TesslB
     rt->dispatch_count += 1;
     TESSL_TRY(cuda_check(rt, cudaGetLastError(), "gemm_q4_mlx_tensorops pre-pass launch"));
 
-    const bool pair = pair_mode() != 0 && m > BM && rt->sm_count >= 2;
+    const bool pair = m >= pair_min_rows() && rt->sm_count >= 2;
     const uint32_t tiles_m = pair ? (m + 2 * BM - 1) / (2 * BM) : (m + BM - 1) / BM;
     const int bn = pick_tile_width(tiles_m, pl.n, pair ? (uint32_t)rt->sm_count / 2 : (uint32_t)rt->sm_count);
 
