@@ -19,7 +19,7 @@ workload. `extra` adds the single-GEMV target shape, the prefill GEMM and the
 other configurations.
 
 With --gpus N > 1 (launched by torchrun, one rank per GPU) the large outputs
-(gate/up, down) are column-sharded over the ranks and all-gathered with NCCL;
+(gate/up) are column-sharded over the ranks and all-gathered with NCCL;
 q/k/v and o_proj are small and run replicated. Total work is fixed: "strong".
 """
 from __future__ import annotations
@@ -183,7 +183,7 @@ def workload_config(n_gpus: int, layers: int = 4):
         "l2": f"weights rotate over {layers} layers' banks ({layers * STEP_WEIGHT_BYTES / 1e6:.0f} MB > 126 MB L2), "
               "one layer per step",
         "parallelism": "single GPU" if n_gpus == 1 else
-        f"gate/up and down column-sharded over {n_gpus} GPUs with NCCL all-gather of bf16 outputs; qkv, o replicated",
+        f"gate/up column-sharded over {n_gpus} GPUs with one all-gather of the bf16 outputs per step over NVLink (see gather); qkv, o, down replicated",
     }
 
 
@@ -216,7 +216,9 @@ class Layer:
         self.o, _ = take(HIDDEN, HIDDEN, False)
         self.gate, self.sh_mid = take(INTER, HIDDEN, True)
         self.up, _ = take(INTER, HIDDEN, True)
-        self.down, self.sh_out = take(HIDDEN, INTER, True)
+        # down has a small output dimension (4096 rows): a slice of it is a few MB per GPU and its
+        # all-gather costs more than it saves, so it runs replicated like q/k/v and o.
+        self.down, self.sh_out = take(HIDDEN, INTER, False)
 
 
 def run_ours(args, rank: int, world: int, local_rank: int):
@@ -239,10 +241,24 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     acts = {n: torch.randn(HIDDEN, device=dev, generator=gen).to(torch.bfloat16) for n in ("x_qkv", "x_o", "x_mlp")}
     qkv_out = torch.empty(QKV, device=dev)
     o_out = torch.empty(HIDDEN, device=dev)
-    mid_local = torch.empty(layers[0].sh_mid.local_rows, device=dev, dtype=torch.bfloat16)
-    mid_full = torch.empty(INTER, device=dev, dtype=torch.bfloat16) if world > 1 else mid_local
+    # N > 1: the gathered gate/up output lives in peer-mapped memory and is exchanged by the
+    # library's own NVLink gather (a few KB per rank: an NCCL all-gather of that size measured
+    # ~14 us per call, more than the sharded GEMV before it); NCCL is the fallback if the
+    # peer-mapped allocation is unavailable.
+    peer = None
+    if world > 1:
+        try:
+            peer = sharded.PeerGather(layers[0].sh_mid.local_rows * 2)
+        except Exception as e:  # noqa: BLE001
+            if rank == 0:
+                print(f"bench: peer-memory gather unavailable ({type(e).__name__}: {e}); using NCCL", file=sys.stderr)
+    if peer is not None:
+        mid_local, mid_full = peer.local(torch.bfloat16), peer.full(torch.bfloat16)
+    else:
+        mid_local = torch.empty(layers[0].sh_mid.local_rows, device=dev, dtype=torch.bfloat16)
+        mid_full = torch.empty(INTER, device=dev, dtype=torch.bfloat16) if world > 1 else mid_local
     y_local = torch.empty(layers[0].sh_out.local_rows, device=dev)
-    y_full = torch.empty(HIDDEN, device=dev) if world > 1 else y_local
+    y_full = torch.empty(HIDDEN, device=dev) if layers[0].sh_out.world > 1 else y_local
     B = nn.GpuBuffer.from_torch
     bufs = {k: B(v) for k, v in acts.items()}
     qkv_b, o_b, midl_b, midf_b, yl_b = B(qkv_out), B(o_out), B(mid_local), B(mid_full), B(y_local)
@@ -257,11 +273,13 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         nn.gemv_q4_mlx_simd(rt, L.qkv, bufs["x_qkv"], qkv_b, sq)
         nn.gemv_q4_mlx_simd(rt, L.o, bufs["x_o"], o_b, so)
         nn.gemv_q4_mlx_gate_up_silu(rt, L.gate, L.up, bufs["x_mlp"], midl_b, sg, True)
-        if world > 1:
+        if peer is not None:
+            peer.run(rt)
+        elif world > 1:
             with torch.cuda.stream(st):
                 sharded.all_gather_rows(mid_local, L.sh_mid, out=mid_full)
         nn.gemv_q4_mlx_simd(rt, L.down, midf_b, yl_b, sd)
-        if world > 1:
+        if L.sh_out.world > 1:
             with torch.cuda.stream(st):
                 sharded.all_gather_rows(y_local, L.sh_out, out=y_full)
             return y_full
@@ -351,7 +369,81 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     rt.set_encode_only(False)
     return dict(torch=torch, dist=dist, nn=nn, rt=rt, st=st, layers=layers, acts=acts, step=step, ms_per_step=ms_per_step,
                 value=value, clocks=clocks.summary(), per_kernel=per_kernel, peaks=peaks, dev=dev,
-                launches_per_step=launches_per_step, n_layers=n_layers, y_local=y_local, bufs=bufs)
+                launches_per_step=launches_per_step + (1 if peer is not None else 0), n_layers=n_layers,
+                y_local=y_local, bufs=bufs, gather="peer memory (tessl_peer_gather)" if peer is not None else "nccl")
+
+
+def measure_sharded_lm_head(ctx, args, world, rank):
+    """N > 1 only: the LM head (151936 x 4096, Q4 g64), rows sharded over the ranks, every rank
+    streaming its slice and one NCCL all-gather of the bf16 logits per call; device time of the
+    slowest rank, whole-job weight bytes per second."""
+    torch, dist, nn, rt, st = ctx["torch"], ctx["dist"], ctx["nn"], ctx["rt"], ctx["st"]
+    from tessl_b200 import sharded
+    rows, cols = 151936, HIDDEN
+    sh = sharded.make_shard(rows, world, rank)
+    per = sharded.slice_rows_per_rank(rows, world)
+    gen = torch.Generator(device="cuda")
+    gen.manual_seed(0x7E55AA + rank)
+    banks, keep = [], []
+    for _ in range(2):  # two rotating slices: 2 x 350 MB / world, beyond L2 up to 4 ranks; smaller slices may sit in L2
+        packed = torch.randint(0, 2**31 - 1, (sh.local_rows, cols // 8), dtype=torch.int32, device="cuda", generator=gen)
+        sc = (torch.rand((sh.local_rows, cols // GROUP), device="cuda", generator=gen) * 0.018 + 0.002).to(torch.bfloat16)
+        sb = torch.stack([sc, (-8.0 * sc.float()).to(torch.bfloat16)], dim=-1).contiguous()
+        keep += [packed, sb]
+        banks.append(nn.Q4MlxBank(nn.GpuBuffer.from_torch(packed), nn.GpuBuffer.from_torch(sb)))
+    x = ctx["bufs"]["x_mlp"]
+    peer = None
+    if ctx.get("gather", "nccl") != "nccl":
+        try:
+            peer = sharded.PeerGather(per * 2)
+        except Exception:  # noqa: BLE001
+            peer = None
+    if peer is not None:
+        y_local, y_full = peer.local(torch.bfloat16), peer.full(torch.bfloat16)
+    else:
+        y_local = torch.zeros(per, device=ctx["dev"], dtype=torch.bfloat16)
+        y_full = torch.empty(per * world, device=ctx["dev"], dtype=torch.bfloat16)
+    yl_b = nn.GpuBuffer.from_torch(y_local)
+    shape = nn.QuantShape(sh.local_rows, cols, GROUP)
+    iters = 8
+
+    def call(i):
+        nn.gemv_q4_mlx_simd(rt, banks[i % 2], x, yl_b, shape, y_as_bf16=True)
+        if peer is not None:
+            peer.run(rt)
+        else:
+            with torch.cuda.stream(st):
+                dist.all_gather_into_tensor(y_full, y_local)
+
+    rt.set_encode_only(True)
+    for i in range(3):
+        call(i)
+    rt.synchronize()
+    torch.cuda.synchronize()
+    dist.barrier()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g, stream=st):
+        for i in range(iters):
+            call(i)
+    best = 1e30
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for rep in range(4):
+        dist.barrier()
+        with torch.cuda.stream(st):
+            a.record(st)
+            g.replay()
+            b.record(st)
+        b.synchronize()
+        if rep:
+            best = min(best, a.elapsed_time(b) / iters)
+    rt.set_encode_only(False)
+    t = torch.tensor([best], device=ctx["dev"])
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    us = float(t.item()) * 1e3
+    nbytes = q4_weight_bytes(rows, cols)
+    return {"us": round(us, 2), "weight_gbs": round(nbytes / us / 1e3, 1), "rows_per_gpu": int(sh.local_rows),
+            "how": "GEMV on this rank's row slice + one all-gather of the bf16 logits ("
+                   + ("peer memory" if peer is not None else "NCCL") + "), both in one CUDA graph"}
 
 
 def measure_e2e(ctx, args):
@@ -568,7 +660,7 @@ def main():
         "warmup": max(args.warmup, 3), "ms_per_step": round(ctx["ms_per_step"], 5), "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "f32 accumulate over bf16 x / Q4 weights", "data": "synthetic",
         "config": workload_config(world, ctx["n_layers"]),
-        "gpu_launches": ctx["launches_per_step"] * args.steps,
+        "gpu_launches": ctx["launches_per_step"] * args.steps, "gather": ctx.get("gather") if world > 1 else None,
         "clocks": ctx["clocks"],
         "frac_of_measured_hbm": round(ctx["value"] / (peaks["hbm_gbs"] * world), 4),
         "frac_of_nominal_8tbs": round(ctx["value"] / (8000.0 * world), 4),
@@ -595,6 +687,8 @@ def main():
         line["cpu_baseline"] = cpu_baseline(args)
     else:
         line["e2e"] = None
+        sharded_head = measure_sharded_lm_head(ctx, args, world, rank)
+        line["extra"] = {f"lm_head 151936x4096 m=1 sharded over {world} GPUs": sharded_head}
     if rank == 0:
         print(json.dumps(line), flush=True)
     if world > 1:

@@ -230,6 +230,26 @@ TESSL_API int32_t tessl_gemm_q4_mlx_tensorops_bf16(TesslRuntime *rt, TesslQ4MlxB
 TESSL_API int32_t tessl_gemm_q4_mlx_tensorops_noalloc(TesslRuntime *rt, TesslQ4MlxBank bank, TesslBuf x_bf16, TesslBuf y,
                                             TesslQuantShape shape, uint32_t m, char *err, size_t err_len);
 
+/* All-gather of per-GPU output slices through NVLink peer memory: NO COUNTERPART IN
+ * THE REFERENCE (a single-device library). For the column-sharded GEMVs, whose
+ * outputs are too small for a library all-gather to be anything but latency.
+ * `buffers[r]` is rank r's gather buffer (world * bytes_per_rank bytes, peer
+ * mapped on this GPU, 16-byte aligned), `flags[r]` rank r's 17 zero-initialised
+ * 32-bit flag words (peer mapped as well). Each rank writes its slice into
+ * buffers[rank] + rank * bytes_per_rank (the GEMV can do that directly), then
+ * every rank makes this call on its own stream; when the call's kernel has
+ * finished, buffers[rank] holds all slices. Calls must be made in the same order
+ * on every rank. The kernel waits for its peers with a ~2 s bound; on expiry the
+ * runtime is poisoned. May be captured in a CUDA graph. */
+typedef struct TesslPeerGather {
+    void *buffers[8];
+    uint32_t *flags[8];
+    uint32_t rank;
+    uint32_t world;
+    uint64_t bytes_per_rank;
+} TesslPeerGather;
+TESSL_API int32_t tessl_peer_gather(TesslRuntime *rt, const TesslPeerGather *gather, char *err, size_t err_len);
+
 /* `Q4Weight::matmul` (src/qwen35_q4.rs:518-561): the M-dispatch policy over one
  * bank of group size 64. m == 0 is a no-op, 1 the GEMV, 2..=8 the small-batch
  * kernel, more the tensor-core GEMM (which refuses a residual). x is bf16

@@ -42,6 +42,11 @@ class QkvOutputs(C.Structure):
     _fields_ = [("q_out", Buf), ("k_out", Buf), ("v_out", Buf)]
 
 
+class PeerGather(C.Structure):
+    _fields_ = [("buffers", C.c_void_p * 8), ("flags", C.c_void_p * 8), ("rank", C.c_uint32), ("world", C.c_uint32),
+                ("bytes_per_rank", C.c_uint64)]
+
+
 _ERR = [C.c_char_p, C.c_size_t]
 _RT = C.c_void_p
 _u32 = C.c_uint32
@@ -79,6 +84,7 @@ SIGNATURES = {
     "tessl_gemm_q4_mlx_tensorops": (C.c_int32, [_RT, Q4MlxBank, Buf, Buf, QuantShape, _u32] + _ERR),
     "tessl_gemm_q4_mlx_tensorops_bf16": (C.c_int32, [_RT, Q4MlxBank, Buf, Buf, QuantShape, _u32] + _ERR),
     "tessl_gemm_q4_mlx_tensorops_noalloc": (C.c_int32, [_RT, Q4MlxBank, Buf, Buf, QuantShape, _u32] + _ERR),
+    "tessl_peer_gather": (C.c_int32, [_RT, C.POINTER(PeerGather)] + _ERR),
     "tessl_q4_weight_matmul": (C.c_int32, [_RT, Q4MlxBank, _u32, _u32, Buf, _u32, Buf, C.POINTER(Buf)] + _ERR),
     "tessl_q4_weight_gate_up_silu": (C.c_int32, [_RT, Q4MlxBank, Q4MlxBank, _u32, _u32, Buf, Buf, _u32] + _ERR),
     "tessl_gemv_q8": (C.c_int32, [_RT, Buf, Buf, Buf, Buf, Buf, _u32, _u32, _u32] + _ERR),

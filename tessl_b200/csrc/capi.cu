@@ -419,6 +419,14 @@ int32_t tessl_gemm_q4_mlx_tensorops_noalloc(TesslRuntime *rt, TesslQ4MlxBank ban
     });
 }
 
+int32_t tessl_peer_gather(TesslRuntime *rt, const TesslPeerGather *gather, char *err, size_t err_len)
+{
+    return guarded(rt, err, err_len, true, [&]() -> tessl::Result {
+        if (!gather) return "peer_gather: null descriptor";
+        return tessl::nn::peer_gather(rt, *gather);
+    });
+}
+
 int32_t tessl_q4_weight_matmul(TesslRuntime *rt, TesslQ4MlxBank bank, uint32_t rows, uint32_t cols, TesslBuf x_bf16,
                                uint32_t m, TesslBuf y, const TesslBuf *resid, char *err, size_t err_len)
 {

@@ -109,3 +109,58 @@ def sharded_matvec(compute: Callable[[RowShard], torch.Tensor], rows: int, m: in
 
 def partition_table(rows: int, world: int, align: int = 8) -> List[Tuple[int, int]]:
     return [shard_rows(rows, world, r, align) for r in range(world)]
+
+
+class PeerGather:
+    """All-gather of this rank's output slice through NVLink peer memory
+    (`tessl_peer_gather`): for slices of a few KB to a few hundred KB, where a
+    library all-gather is pure latency.
+
+    Holds one gather buffer of `world * bytes_per_rank` bytes per rank in
+    symmetric memory (torch's `_symmetric_memory`: peer-mapped allocations, used
+    here only as the allocator and for the address exchange). The producer writes
+    into `local(dtype)` (this rank's part of its own buffer); `run(rt)` encodes
+    the gather on the runtime's stream; afterwards `full(dtype)` holds every
+    rank's slice. Every rank must call `run` the same number of times in the
+    same order."""
+
+    def __init__(self, bytes_per_rank: int, group=None):
+        import torch.distributed._symmetric_memory as symm_mem
+
+        from . import capi
+        if bytes_per_rank % 16:
+            raise ValueError("bytes_per_rank must be a multiple of 16")
+        group = group if group is not None else dist.group.WORLD
+        self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        if self.world > 8:
+            raise ValueError("PeerGather serves the GPUs of one node (at most 8)")
+        self.bytes_per_rank = bytes_per_rank
+        dev = torch.device("cuda", torch.cuda.current_device())
+        self.buf = symm_mem.empty(self.world * bytes_per_rank, dtype=torch.uint8, device=dev)
+        self.flags = symm_mem.empty(32, dtype=torch.int32, device=dev)
+        self.buf.zero_()
+        self.flags.zero_()
+        torch.cuda.synchronize()
+        self._hb = symm_mem.rendezvous(self.buf, group)
+        self._hf = symm_mem.rendezvous(self.flags, group)
+        dist.barrier(group)  # every rank's flags are zero before anyone can signal
+        desc = capi.PeerGather()
+        for r in range(self.world):
+            desc.buffers[r] = int(self._hb.buffer_ptrs[r])
+            desc.flags[r] = int(self._hf.buffer_ptrs[r])
+        desc.rank, desc.world, desc.bytes_per_rank = self.rank, self.world, bytes_per_rank
+        self._desc = desc
+
+    def local(self, dtype) -> torch.Tensor:
+        """This rank's slice of its own gather buffer, as a 1-D tensor of `dtype`."""
+        b = self.bytes_per_rank
+        return self.buf[self.rank * b:(self.rank + 1) * b].view(dtype)
+
+    def full(self, dtype) -> torch.Tensor:
+        return self.buf.view(dtype)
+
+    def run(self, rt) -> None:
+        import ctypes
+
+        from . import capi
+        capi.call("tessl_peer_gather", rt.handle, ctypes.byref(self._desc))

@@ -1,0 +1,98 @@
+"""`tessl_peer_gather`: the NVLink peer-memory all-gather behind the column-sharded
+GEMVs (no counterpart in the reference, a single-device library).
+
+On one GPU only the argument checks and the world == 1 no-op can run; with two or
+more GPUs two ranks (child processes, NCCL only for the rendezvous, NVLS off) gather
+changing patterns several times and compare every byte.
+"""
+import ctypes
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+from gpu_util import rt  # noqa: F401
+from tessl_b200 import capi, nn
+
+pytestmark = pytest.mark.gpu
+
+
+def _desc(world, rank, nbytes, bufs, flags):
+    d = capi.PeerGather()
+    for r in range(8):
+        d.buffers[r] = bufs[r] if r < len(bufs) else None
+        d.flags[r] = flags[r] if r < len(flags) else None
+    d.rank, d.world, d.bytes_per_rank = rank, world, nbytes
+    return d
+
+
+def test_refusals_and_single_rank_noop(rt):
+    buf = rt.alloc_buffer(4096)
+    flg = rt.alloc_buffer(128)
+    rt.take_dispatch_count()
+    bad = [
+        (_desc(0, 0, 64, [buf.ptr], [flg.ptr]), "outside 1..8"),
+        (_desc(9, 0, 64, [buf.ptr] * 8, [flg.ptr] * 8), "outside 1..8"),
+        (_desc(2, 2, 64, [buf.ptr] * 2, [flg.ptr] * 2), "outside world"),
+        (_desc(2, 0, 24, [buf.ptr] * 2, [flg.ptr] * 2), "multiple of 16"),
+        (_desc(2, 0, 64, [buf.ptr, None], [flg.ptr] * 2), "null buffer or flag"),
+        (_desc(2, 0, 64, [buf.ptr, buf.ptr + 4], [flg.ptr] * 2), "16-byte aligned"),
+    ]
+    for d, text in bad:
+        with pytest.raises(capi.TesslError, match=text):
+            capi.call("tessl_peer_gather", rt.handle, ctypes.byref(d))
+    with pytest.raises(capi.TesslError, match="null descriptor"):
+        capi.call("tessl_peer_gather", rt.handle, None)
+    # one rank: nothing to exchange, nothing launched
+    capi.call("tessl_peer_gather", rt.handle, ctypes.byref(_desc(1, 0, 64, [buf.ptr], [flg.ptr])))
+    assert rt.take_dispatch_count() == 0
+
+
+_CHILD = r"""
+import os, sys
+import numpy as np, torch, torch.distributed as dist
+sys.path.insert(0, os.environ["TESSL_REPO"])
+from tessl_b200 import nn, sharded
+rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+torch.cuda.set_device(rank)
+dist.init_process_group("nccl", device_id=torch.device("cuda", rank))
+rt = nn.Runtime(rank)
+n = 6144  # bf16 elements per rank
+pg = sharded.PeerGather(n * 2)
+st = torch.cuda.ExternalStream(rt.stream, device=rank)
+for call in range(5):
+    with torch.cuda.stream(st):
+        pg.local(torch.int16).copy_(torch.arange(n, device="cuda", dtype=torch.int32).add_(1000 * rank + 7 * call).to(torch.int16))
+    pg.run(rt)   # synchronous: returns when this rank's buffer holds every slice
+    got = pg.full(torch.int16).cpu().numpy().reshape(world, n)
+    for r in range(world):
+        want = (np.arange(n, dtype=np.int32) + 1000 * r + 7 * call).astype(np.int16)
+        assert np.array_equal(got[r], want), (rank, call, r)
+    dist.barrier()   # nobody starts overwriting its slice before everyone has checked
+assert not rt.is_poisoned()
+dist.destroy_process_group()
+print("peer gather ok", rank)
+"""
+
+
+def test_two_ranks_gather_changing_patterns():
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    repo = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, TESSL_REPO=repo, MASTER_ADDR="127.0.0.1", MASTER_PORT="29533", WORLD_SIZE="2",
+               NCCL_NVLS_ENABLE="0", TORCH_SYMM_MEM_DISABLE_MULTICAST="1")
+    procs = [subprocess.Popen([sys.executable, "-c", _CHILD], env=dict(env, RANK=str(r)), stdout=subprocess.PIPE,
+                              stderr=subprocess.STDOUT, text=True) for r in range(2)]
+    outs = []
+    for p in procs:
+        try:
+            out, _ = p.communicate(timeout=240)
+        except subprocess.TimeoutExpired:
+            p.kill()
+            out, _ = p.communicate()
+        outs.append((p.returncode, out))
+    for code, out in outs:
+        assert code == 0 and "peer gather ok" in out, out[-2000:]
