@@ -247,11 +247,23 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     # peer-mapped allocation is unavailable.
     peer = None
     if world > 1:
+        why = ""
         try:
             peer = sharded.PeerGather(layers[0].sh_mid.local_rows * 2)
+            probe = nn.Runtime(local_rank)  # a trial exchange on a runtime of its own: a failure poisons only that one
+            try:
+                for _ in range(3):
+                    peer.run(probe)
+            finally:
+                probe.close()
         except Exception as e:  # noqa: BLE001
+            peer, why = None, f"{type(e).__name__}: {e}"
+        agreed = torch.tensor([1 if peer is not None else 0], device=dev)
+        dist.all_reduce(agreed, op=dist.ReduceOp.MIN)
+        if int(agreed.item()) == 0:
+            peer = None
             if rank == 0:
-                print(f"bench: peer-memory gather unavailable ({type(e).__name__}: {e}); using NCCL", file=sys.stderr)
+                print(f"bench: peer-memory gather unavailable ({why or 'on another rank'}); using NCCL", file=sys.stderr)
     if peer is not None:
         mid_local, mid_full = peer.local(torch.bfloat16), peer.full(torch.bfloat16)
     else:

@@ -234,12 +234,12 @@ TESSL_API int32_t tessl_gemm_q4_mlx_tensorops_noalloc(TesslRuntime *rt, TesslQ4M
  * THE REFERENCE (a single-device library). For the column-sharded GEMVs, whose
  * outputs are too small for a library all-gather to be anything but latency.
  * `buffers[r]` is rank r's gather buffer (world * bytes_per_rank bytes, peer
- * mapped on this GPU, 16-byte aligned), `flags[r]` rank r's 17 zero-initialised
+ * mapped on this GPU, 16-byte aligned), `flags[r]` rank r's 18 zero-initialised
  * 32-bit flag words (peer mapped as well). Each rank writes its slice into
  * buffers[rank] + rank * bytes_per_rank (the GEMV can do that directly), then
  * every rank makes this call on its own stream; when the call's kernel has
  * finished, buffers[rank] holds all slices. Calls must be made in the same order
- * on every rank. The kernel waits for its peers with a ~2 s bound; on expiry the
+ * on every rank. The kernel waits for its peers with a ~0.5 s bound; on expiry the
  * runtime is poisoned. May be captured in a CUDA graph. */
 typedef struct TesslPeerGather {
     void *buffers[8];

@@ -13,10 +13,14 @@
 //      for every peer's completion.
 // Flags are monotonically increasing call numbers kept in peer-mapped memory
 // (`flags` of rank r: [0, 8) arrivals by source rank, [8, 16) completions by
-// source rank, [16] this rank's own call counter), so the same launch can be
-// replayed from a CUDA graph. Every wait is bounded (~2 s); on expiry the
+// source rank, [16] this rank's own call counter, [17] a ticket counter of the
+// call's thread blocks), so the same launch can be replayed from a CUDA graph.
+// Larger slices are copied by several thread blocks; the last one to finish its
+// part (by ticket) does the completion handshake. Every wait is bounded (~2 s); on expiry the
 // runtime's status word is set and the kernel returns. There is no counterpart
 // in the reference (a single-device library).
+#include <algorithm>
+
 #include "runtime.h"
 
 namespace tessl {
@@ -29,6 +33,10 @@ struct PeerGatherParams {
     uint64_t bytes_per_rank;  // multiple of 16
     uint32_t *status;
 };
+
+// Bound of every wait for a peer: ~0.5 s. The peers reach the same call within microseconds when they run
+// the same stream of work; a rank that is this late is treated as lost and the runtime is poisoned.
+constexpr long long kWaitClocks = 1000000000ll;
 
 __device__ __forceinline__ void st_release_sys(uint32_t *p, uint32_t v)
 {
@@ -49,7 +57,7 @@ __device__ __forceinline__ bool wait_peers(const PeerGatherParams &p, uint32_t b
         const uint32_t *f = p.flags[p.rank] + base + threadIdx.x;
         const long long t0 = clock64();
         while ((int32_t)(ld_acquire_sys(f) - seq) < 0) {
-            if (clock64() - t0 > 4000000000ll) {
+            if (clock64() - t0 > kWaitClocks) {
                 *(volatile uint32_t *)p.status = (0x50u << 24) | (code << 16) | threadIdx.x;
                 ok_ = false;
                 break;
@@ -69,24 +77,32 @@ __global__ void __launch_bounds__(1024, 1) peer_gather_kernel(const PeerGatherPa
     asm volatile("griddepcontrol.launch_dependents;");
     asm volatile("griddepcontrol.wait;" ::: "memory");
     uint32_t *mine = p.flags[p.rank];
-    const uint32_t seq = mine[16] + 1;  // this call's number, the same on every rank
-    // 1. arrival
-    if (threadIdx.x < p.world && threadIdx.x != p.rank) st_release_sys(p.flags[threadIdx.x] + p.rank, seq);
+    // This call's number, the same on every rank. [16] is only advanced by the call's last block, after every
+    // block has read it here (a block takes its ticket after this read).
+    const uint32_t seq = *(volatile uint32_t *)(mine + 16) + 1;
+    // 1. arrival: block 0 tells the peers, every block waits for theirs
+    if (blockIdx.x == 0 && threadIdx.x < p.world && threadIdx.x != p.rank)
+        st_release_sys(p.flags[threadIdx.x] + p.rank, seq);
     if (!wait_peers(p, 0, seq, 1)) return;
-    // 2. this rank's slice into every peer's buffer
+    // 2. this rank's slice into every peer's buffer, the blocks sharing the 16-byte pieces
     const uint64_t n16 = p.bytes_per_rank / 16;
     const uint4 *src = reinterpret_cast<const uint4 *>(p.buf[p.rank] + (size_t)p.rank * p.bytes_per_rank);
-    for (uint64_t i = threadIdx.x; i < n16; i += blockDim.x) {
+    for (uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n16; i += (uint64_t)gridDim.x * blockDim.x) {
         const uint4 v = src[i];
         for (uint32_t r = 0; r < p.world; ++r)
             if (r != p.rank) reinterpret_cast<uint4 *>(p.buf[r] + (size_t)p.rank * p.bytes_per_rank)[i] = v;
     }
     __threadfence_system();
     __syncthreads();
-    // 3. completion
+    // 3. completion, by the last block to get here
+    __shared__ uint32_t ticket;
+    if (threadIdx.x == 0) ticket = atomicAdd(mine + 17, 1u);
+    __syncthreads();
+    if (ticket != gridDim.x - 1) return;
+    __threadfence();  // the other blocks' stores (fenced at system scope before their tickets) precede the signal
     if (threadIdx.x < p.world && threadIdx.x != p.rank) st_release_sys(p.flags[threadIdx.x] + 8 + p.rank, seq);
     if (!wait_peers(p, 8, seq, 2)) return;
-    if (threadIdx.x == 0) mine[16] = seq;
+    if (threadIdx.x == 0) mine[17] = 0, mine[16] = seq;
 }
 
 }  // namespace
@@ -110,7 +126,10 @@ Result peer_gather(TesslRuntime *rt, const TesslPeerGather &g)
     p.rank = g.rank, p.world = g.world, p.bytes_per_rank = g.bytes_per_rank;
     p.status = rt->status_dev;
     cudaLaunchConfig_t lc{};
-    lc.gridDim = dim3(1), lc.blockDim = dim3(1024), lc.dynamicSmemBytes = 0;
+    // one block per 32 KiB of slice, at most 16: a few KB go fastest from one block, the LM head's
+    // hundreds of KB need several to fill the link
+    const uint32_t blocks = (uint32_t)std::min<uint64_t>(16, std::max<uint64_t>(1, g.bytes_per_rank / 32768));
+    lc.gridDim = dim3(blocks), lc.blockDim = dim3(1024), lc.dynamicSmemBytes = 0;
     lc.stream = rt->stream;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
