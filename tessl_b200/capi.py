@@ -8,6 +8,7 @@ library is missing or its ABI differs, importing fails loudly.
 from __future__ import annotations
 
 import ctypes as C
+import threading
 from pathlib import Path
 
 ABI_VERSION = 1
@@ -120,9 +121,21 @@ def load() -> C.CDLL:
 ERR_LEN = 1024
 
 
+_fn_cache: dict = {}
+_err_local = threading.local()
+
+
 def call(name: str, *args) -> None:
-    """Call a status-returning entry; raise TesslError with the library's message."""
-    err = C.create_string_buffer(ERR_LEN)
-    st = getattr(load(), name)(*args, err, ERR_LEN)
+    """Call a status-returning entry; raise TesslError with the library's message.
+
+    The error buffer is per thread and reused (a decode loop makes several calls per
+    token; allocating 1 KiB each time showed up in the end-to-end timing)."""
+    fn = _fn_cache.get(name)
+    if fn is None:
+        fn = _fn_cache[name] = getattr(load(), name)
+    err = getattr(_err_local, "buf", None)
+    if err is None:
+        err = _err_local.buf = C.create_string_buffer(ERR_LEN)
+    st = fn(*args, err, ERR_LEN)
     if st != TESSL_OK:
         raise TesslError(st, err.value.decode("utf-8", "replace"))

@@ -32,7 +32,11 @@ class QuantShape:
     group_size: int
 
     def c(self) -> _CShape:
-        return _CShape(self.rows, self.cols, self.group_size)
+        cached = self.__dict__.get("_c")  # the ctypes struct is built once (frozen dataclass: fields never change)
+        if cached is None:
+            cached = _CShape(self.rows, self.cols, self.group_size)
+            object.__setattr__(self, "_c", cached)
+        return cached
 
 
 class GpuBuffer:
@@ -43,6 +47,7 @@ class GpuBuffer:
 
     def __init__(self, ptr: int, nbytes: int, owner=None, rt: "Runtime | None" = None):
         self.ptr, self.nbytes, self._owner, self._rt = int(ptr or 0), int(nbytes), owner, rt
+        self._c = None  # ctypes view, built on first use
 
     @staticmethod
     def from_torch(t) -> "GpuBuffer":
@@ -56,15 +61,23 @@ class GpuBuffer:
         return GpuBuffer(self.ptr + byte_offset, nbytes, owner=self)
 
     def c(self) -> Buf:
-        return Buf(self.ptr, self.nbytes)
+        b = self._c
+        if b is None or b.ptr != (self.ptr or None) or b.nbytes != self.nbytes:
+            b = self._c = Buf(self.ptr, self.nbytes)
+        return b
 
     def write(self, data: np.ndarray, byte_offset: int = 0) -> None:
         a = np.ascontiguousarray(data)
         capi.call("tessl_buffer_write", self._runtime().handle, self.c(), byte_offset,
                   a.ctypes.data_as(C.c_void_p), a.nbytes)
 
-    def read(self, dtype, count: int, byte_offset: int = 0) -> np.ndarray:
-        out = np.empty(count, dtype)
+    def read(self, dtype, count: int, byte_offset: int = 0, out: "np.ndarray | None" = None) -> np.ndarray:
+        """Reads `count` elements; into `out` if given (e.g. a view of pinned host memory, which makes the
+        copy a plain DMA instead of a staged one)."""
+        if out is None:
+            out = np.empty(count, dtype)
+        elif out.dtype != np.dtype(dtype) or out.size != count or not out.flags.c_contiguous:
+            raise ValueError("out must be a contiguous array of `count` elements of `dtype`")
         capi.call("tessl_buffer_read", self._runtime().handle, self.c(), byte_offset,
                   out.ctypes.data_as(C.c_void_p), out.nbytes)
         return out
@@ -90,7 +103,12 @@ class Q4MlxBank:
     scales_biases: GpuBuffer
 
     def c(self) -> _CBank:
-        return _CBank(self.packed.c(), self.scales_biases.c())
+        key = (self.packed.ptr, self.packed.nbytes, self.scales_biases.ptr, self.scales_biases.nbytes)
+        cached = self.__dict__.get("_c")
+        if cached is None or cached[0] != key:
+            cached = (key, _CBank(self.packed.c(), self.scales_biases.c()))
+            self.__dict__["_c"] = cached
+        return cached[1]
 
 
 @dataclass
