@@ -224,10 +224,10 @@ bool mma_ok(const Q4GemvParams &p)
     return true;
 }
 
-template <int SW, int WPG, int NB, bool BATCH>
+template <int SW, int WPG, int NB, bool BATCH, bool Q8 = false>
 Result launch_mma_one(TesslRuntime *rt, const Q4GemvParams &p, int m)
 {
-    auto kernel = q4m::q4_gemv_mma_kernel<SW, WPG, NB, BATCH>;
+    auto kernel = q4m::q4_gemv_mma_kernel<SW, WPG, NB, BATCH, Q8>;
     constexpr uint32_t RPB = 16 / NB;
     q4m::Params mp{};
     uint32_t rb = 0;
@@ -312,6 +312,12 @@ Result launch_mma(TesslRuntime *rt, const Q4GemvParams &p, int m, int nb)
     }
     if (wpg == 1) return launch_mma_sw<2, 1>(rt, p, m, nb);
     return launch_mma_sw<2, 2>(rt, p, m, nb);
+}
+
+template <int SW, int WPG>
+Result launch_mma_q8_sw(TesslRuntime *rt, const Q4GemvParams &p, int m)
+{
+    return launch_mma_one<SW, WPG, 1, true, true>(rt, p, m);
 }
 
 /// The staged kernel needs every bulk copy 16-byte aligned and sized.
@@ -418,6 +424,45 @@ Result check_alignment(const TesslQ4MlxBank &b, const std::string &what)
 }  // namespace
 
 namespace nn {
+
+/// MLX Q8 (unsigned codes, bf16 pairs, bf16 x, M <= 8) on the tensor-core GEMV kernel: a row of `cols`
+/// codes runs as a row of 2 cols nibbles with groups of 2 group_size. `*handled` is false when the shape is
+/// not one the kernel is built for (the caller then uses its FMA-pipe kernel).
+Result q8_mlx_mma(TesslRuntime *rt, const TesslBuf &codes, const TesslBuf &sb, const TesslBuf &x_bf16, const TesslBuf &y,
+                  uint32_t rows, uint32_t cols, uint32_t group_size, uint32_t m, OutKind out, bool *handled)
+{
+    *handled = false;
+    if (!mma_enabled()) return ok();
+    // One vector stays on the FMA-pipe kernel (14336 x 4096: 19.0 us there, 19.9 us here); from two rows on
+    // this kernel costs the same as one (23 us at M = 4 and 8 against 35 and 55 us).
+    if (m < 2) return ok();
+    if (cols != 512 && cols != 1024 && cols != 2048 && cols != 4096) return ok();
+    if (group_size != 32 && group_size != 64) return ok();
+    if (((uintptr_t)sb.ptr & 15u) != 0 || ((uintptr_t)x_bf16.ptr & 7u) != 0) return ok();
+    if (((2 * cols / 16) / (2 * group_size)) == 0) return ok();  // a warp's slice holds whole groups
+    *handled = true;
+    Q4GemvParams p{};
+    p.nseg = 1;
+    p.seg[0] = Q4Seg{};
+    p.seg[0].packed0 = static_cast<const uint8_t *>(codes.ptr);
+    p.seg[0].sb0 = static_cast<const uint32_t *>(sb.ptr);
+    p.seg[0].out = y.ptr;
+    p.seg[0].rows = rows;
+    p.x = static_cast<const uint16_t *>(x_bf16.ptr);
+    p.cols = 2 * cols;
+    p.group_shift = log2_u32(2 * group_size);
+    p.epi = EPI_STORE;
+    p.out_bf16 = out == OUT_BF16;
+    const int sw = (int)(p.cols / 512);
+    const bool g64 = group_size == 64;  // 128 nibbles: 4 words per lane and group; 32 codes: 2
+    switch (sw) {
+    case 2: return g64 ? launch_mma_q8_sw<2, 2>(rt, p, (int)m) : launch_mma_q8_sw<2, 2>(rt, p, (int)m);
+    case 4: return g64 ? launch_mma_q8_sw<4, 4>(rt, p, (int)m) : launch_mma_q8_sw<4, 2>(rt, p, (int)m);
+    case 8: return g64 ? launch_mma_q8_sw<8, 4>(rt, p, (int)m) : launch_mma_q8_sw<8, 2>(rt, p, (int)m);
+    default: return g64 ? launch_mma_q8_sw<16, 4>(rt, p, (int)m) : launch_mma_q8_sw<16, 2>(rt, p, (int)m);
+    }
+}
+
 
 Result gemv_q4_mlx_simd(TesslRuntime *rt, const TesslQ4MlxBank &bank, const TesslBuf &x_bf16, const TesslBuf &y,
                         const TesslQuantShape &shape, uint32_t layout, const TesslBuf *resid, OutKind out)

@@ -302,6 +302,12 @@ Result gemm_q8_mlx(TesslRuntime *rt, const TesslBuf &codes, const TesslBuf &sb, 
     TESSL_TRY(require_disjoint_writes(entry, writes, 1, reads, 3));
     TESSL_TRY(require_aligned16(codes, std::string(entry) + " codes"));
     TESSL_TRY(require_aligned16(x_bf16, std::string(entry) + " x_bf16"));
+    {
+        // rows of 512 .. 4096 codes in groups of 32 or 64: the tensor-core GEMV kernel (q4_gemv_mma.cuh)
+        bool handled = false;
+        TESSL_TRY(q8_mlx_mma(rt, codes, sb, x_bf16, y, shape.rows, shape.cols, shape.group_size, m, out, &handled));
+        if (handled) return ok();
+    }
     Q8Params p{};
     p.codes = static_cast<const uint8_t *>(codes.ptr);
     p.sb = static_cast<const uint32_t *>(sb.ptr);

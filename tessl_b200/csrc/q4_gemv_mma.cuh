@@ -119,7 +119,10 @@ __device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1
 /// WPG: words of one lane per quantization group (G / 32).
 /// NB: banks per row block (2 = gate/up: rows 0-7 of the MMA are gate rows, 8-15 the same rows of up).
 /// BATCH: the 8 MMA columns are distinct batch rows (M >= 2) instead of 8 copies of one vector.
-template <int SW, int WPG, int NB, bool BATCH>
+/// Q8: the rows hold 8-bit codes. A code c = 16 h + l is taken as its two nibbles l, h against the
+///     activations x and 16 x (exact in bf16), so a row of K codes runs as a row of 2 K nibbles:
+///     `cols` and the group size are given in nibbles (2 K, 2 G), x has cols / 2 elements per row.
+template <int SW, int WPG, int NB, bool BATCH, bool Q8 = false>
 __global__ void __launch_bounds__(kThreads, TESSL_GEMV_MMA_MIN_BLOCKS) q4_gemv_mma_kernel(const Params p)
 {
     asm volatile("griddepcontrol.launch_dependents;");
@@ -321,20 +324,35 @@ __global__ void __launch_bounds__(kThreads, TESSL_GEMV_MMA_MIN_BLOCKS) q4_gemv_m
         float xs[NGS];  // group sums of the activations: column g (BATCH) or the vector (M = 1)
         {
             const uint32_t n = BATCH ? min(g, p.m - 1) : 0u;
-            const uint16_t *xrow = p.x + (size_t)n * K;
+            const uint16_t *xrow = p.x + (size_t)n * (Q8 ? K / 2 : K);
 #pragma unroll
             for (int jj = 0; jj < NGS; ++jj) {
                 float part = 0.0f;
 #pragma unroll
                 for (int u = 0; u < WPG; ++u) {
                     const uint32_t k = k0 + jj * G + t * (G / 4) + 8 * u;
-                    const uint4 r = __ldg(reinterpret_cast<const uint4 *>(xrow + k));
-                    xb[jj * WPG + u][0] = __byte_perm(r.x, r.z, 0x5410);  // x0, x4
-                    xb[jj * WPG + u][1] = __byte_perm(r.x, r.z, 0x7632);  // x1, x5
-                    xb[jj * WPG + u][2] = __byte_perm(r.y, r.w, 0x5410);  // x2, x6
-                    xb[jj * WPG + u][3] = __byte_perm(r.y, r.w, 0x7632);  // x3, x7
-                    part += (dev::bf16_lo(r.x) + dev::bf16_hi(r.x)) + (dev::bf16_lo(r.y) + dev::bf16_hi(r.y));
-                    part += (dev::bf16_lo(r.z) + dev::bf16_hi(r.z)) + (dev::bf16_lo(r.w) + dev::bf16_hi(r.w));
+                    if constexpr (Q8) {
+                        // the word's 8 nibbles are the low and high halves of 4 codes: nibble pairs (0,4), (1,5),
+                        // (2,6), (3,7) = low of codes 0,2 | high of codes 0,2 | low of 1,3 | high of 1,3
+                        const uint2 r = __ldg(reinterpret_cast<const uint2 *>(xrow + k / 2));
+                        const float x0 = dev::bf16_lo(r.x), x1 = dev::bf16_hi(r.x), x2 = dev::bf16_lo(r.y), x3 = dev::bf16_hi(r.y);
+                        auto pack16 = [](float a, float b) {  // (16 a, 16 b) as bf16: exact, a power of two
+                            return (__float_as_uint(16.0f * a) >> 16) | (__float_as_uint(16.0f * b) & 0xffff0000u);
+                        };
+                        xb[jj * WPG + u][0] = __byte_perm(r.x, r.y, 0x5410);  // x0, x2
+                        xb[jj * WPG + u][1] = pack16(x0, x2);
+                        xb[jj * WPG + u][2] = __byte_perm(r.x, r.y, 0x7632);  // x1, x3
+                        xb[jj * WPG + u][3] = pack16(x1, x3);
+                        part += (x0 + x1) + (x2 + x3);
+                    } else {
+                        const uint4 r = __ldg(reinterpret_cast<const uint4 *>(xrow + k));
+                        xb[jj * WPG + u][0] = __byte_perm(r.x, r.z, 0x5410);  // x0, x4
+                        xb[jj * WPG + u][1] = __byte_perm(r.x, r.z, 0x7632);  // x1, x5
+                        xb[jj * WPG + u][2] = __byte_perm(r.y, r.w, 0x5410);  // x2, x6
+                        xb[jj * WPG + u][3] = __byte_perm(r.y, r.w, 0x7632);  // x3, x7
+                        part += (dev::bf16_lo(r.x) + dev::bf16_hi(r.x)) + (dev::bf16_lo(r.y) + dev::bf16_hi(r.y));
+                        part += (dev::bf16_lo(r.z) + dev::bf16_hi(r.z)) + (dev::bf16_lo(r.w) + dev::bf16_hi(r.w));
+                    }
                 }
                 part += __shfl_xor_sync(0xffffffffu, part, 1);
                 part += __shfl_xor_sync(0xffffffffu, part, 2);
@@ -350,6 +368,8 @@ __global__ void __launch_bounds__(kThreads, TESSL_GEMV_MMA_MIN_BLOCKS) q4_gemv_m
                 xs1[jj] = __shfl_sync(0xffffffffu, xs[jj], (2 * t + 1) * 4);
             }
         }
+        // what the 128 + q trick adds to a group's dot: 128 per nibble, i.e. 128 (x + 16 x) per code when Q8
+        constexpr float kOffset = Q8 ? -128.0f * 17.0f : -128.0f;
         const uint32_t w_off = (k0 >> 1) + t * (G / 8);  // byte offset of the lane's first word within a row
         const uint32_t sb_off = (k0 >> p.group_shift) * 4;
 
@@ -417,10 +437,10 @@ __global__ void __launch_bounds__(kThreads, TESSL_GEMV_MMA_MIN_BLOCKS) q4_gemv_m
                     const uint32_t pl = lds32(sb_lo + jj * 4), ph2 = lds32(sb_hi + jj * 4);
                     const float sl = dev::bf16_lo(pl), bl = dev::bf16_hi(pl), sh = dev::bf16_lo(ph2), bh = dev::bf16_hi(ph2);
                     const int cls = jj & 3;  // a constant once the loop is unrolled
-                    acc[0][cls] = fmaf(sl, fmaf(-128.0f, xs0[jj], d[jj][0]), fmaf(bl, xs0[jj], acc[0][cls]));
-                    acc[1][cls] = fmaf(sl, fmaf(-128.0f, xs1[jj], d[jj][1]), fmaf(bl, xs1[jj], acc[1][cls]));
-                    acc[2][cls] = fmaf(sh, fmaf(-128.0f, xs0[jj], d[jj][2]), fmaf(bh, xs0[jj], acc[2][cls]));
-                    acc[3][cls] = fmaf(sh, fmaf(-128.0f, xs1[jj], d[jj][3]), fmaf(bh, xs1[jj], acc[3][cls]));
+                    acc[0][cls] = fmaf(sl, fmaf(kOffset, xs0[jj], d[jj][0]), fmaf(bl, xs0[jj], acc[0][cls]));
+                    acc[1][cls] = fmaf(sl, fmaf(kOffset, xs1[jj], d[jj][1]), fmaf(bl, xs1[jj], acc[1][cls]));
+                    acc[2][cls] = fmaf(sh, fmaf(kOffset, xs0[jj], d[jj][2]), fmaf(bh, xs0[jj], acc[2][cls]));
+                    acc[3][cls] = fmaf(sh, fmaf(kOffset, xs1[jj], d[jj][3]), fmaf(bh, xs1[jj], acc[3][cls]));
                 } else {
                     dlo[jj] = d[jj][0], dhi[jj] = d[jj][2];  // every column holds the same vector: d[1] == d[0]
                 }
@@ -448,8 +468,8 @@ __global__ void __launch_bounds__(kThreads, TESSL_GEMV_MMA_MIN_BLOCKS) q4_gemv_m
                     const uint32_t jj = 4 * q + t;
                     if (jj < (uint32_t)NGS) {
                         const uint32_t pl = lds32(sb_lo + jj * 4), ph2 = lds32(sb_hi + jj * 4);
-                        vlo = fmaf(dev::bf16_lo(pl), fmaf(-128.0f, xg, dl), fmaf(dev::bf16_hi(pl), xg, vlo));
-                        vhi = fmaf(dev::bf16_lo(ph2), fmaf(-128.0f, xg, dh), fmaf(dev::bf16_hi(ph2), xg, vhi));
+                        vlo = fmaf(dev::bf16_lo(pl), fmaf(kOffset, xg, dl), fmaf(dev::bf16_hi(pl), xg, vlo));
+                        vhi = fmaf(dev::bf16_lo(ph2), fmaf(kOffset, xg, dh), fmaf(dev::bf16_hi(ph2), xg, vhi));
                     }
                 }
                 vlo += __shfl_xor_sync(0xffffffffu, vlo, 1), vhi += __shfl_xor_sync(0xffffffffu, vhi, 1);
