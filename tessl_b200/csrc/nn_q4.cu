@@ -629,6 +629,35 @@ Result swiglu(TesslRuntime *rt, const TesslBuf &gate, const TesslBuf &up, const 
     return cuda_check(rt, cudaGetLastError(), "swiglu launch");
 }
 
+/// A validated prefill call with few rows, run as batches of up to 8 rows on the tensor-core GEMV kernel:
+/// up to 24 rows that is faster than the prefill GEMM, whose 256-row tile would be mostly padding
+/// (12288 x 4096: 9.3 us per batch of 8 against 34.6 us for any m <= 64). `*handled` is false when the shape
+/// is not one that kernel is built for.
+Result prefill_as_small_batches(TesslRuntime *rt, const TesslQ4MlxBank &bank, const TesslBuf &x_bf16, const TesslBuf &y,
+                                const TesslQuantShape &shape, uint32_t m, OutKind out, bool *handled)
+{
+    *handled = false;
+    if (m == 0 || m > 24) return ok();
+    Q4GemvParams probe{};
+    probe.nseg = 1;
+    probe.seg[0] = make_seg(bank, nullptr, y, nullptr, shape.rows);
+    probe.cols = shape.cols;
+    probe.group_shift = log2_u32(shape.group_size);
+    if (!mma_ok(probe)) return ok();
+    *handled = true;
+    const size_t esz = out == OUT_BF16 ? 2 : 4;
+    for (uint32_t b = 0; b < m; b += 8) {
+        const uint32_t mb = std::min<uint32_t>(8u, m - b);
+        Q4GemvParams p = probe;
+        p.seg[0].out = static_cast<char *>(y.ptr) + (size_t)b * shape.rows * esz;
+        p.x = static_cast<const uint16_t *>(x_bf16.ptr) + (size_t)b * shape.cols;
+        p.epi = EPI_STORE;
+        p.out_bf16 = out == OUT_BF16;
+        TESSL_TRY(launch_q4_gemv(rt, p, (int)mb, 1));
+    }
+    return ok();
+}
+
 Result gemm_q4_mlx(TesslRuntime *rt, const TesslQ4MlxBank &bank, const TesslBuf &x_bf16, const TesslBuf &y,
                    const TesslQuantShape &shape, uint32_t m, uint32_t layout, const TesslBuf *resid, OutKind out)
 {

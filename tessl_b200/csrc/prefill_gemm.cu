@@ -648,6 +648,11 @@ Result gemm_q4_mlx_tensorops(TesslRuntime *rt, const TesslQ4MlxBank &bank, const
     bool empty = false;
     TESSL_TRY(prefill_validate(bank, x_bf16, y, shape, m, out, &pl, &empty));
     if (empty) return ok();
+    {
+        bool handled = false;  // a few rows: batches of 8 on the tensor-core GEMV kernel
+        TESSL_TRY(prefill_as_small_batches(rt, bank, x_bf16, y, shape, m, out, &handled));
+        if (handled) return ok();
+    }
     // Scratch: the augmented f16 activations [m, k_aug] and the row scales [m].
     void *scratch = nullptr;
     TESSL_TRY(scratch_reserve(rt, pl.need, &scratch));
@@ -677,6 +682,11 @@ Result gemm_q4_mlx_tensorops_noalloc(TesslRuntime *rt, const TesslQ4MlxBank &ban
     bool empty = false;
     TESSL_TRY(prefill_validate(bank, x_bf16, y, shape, m, out, &pl, &empty));
     if (empty) return ok();
+    {
+        bool handled = false;  // needs no scratch at all
+        TESSL_TRY(prefill_as_small_batches(rt, bank, x_bf16, y, shape, m, out, &handled));
+        if (handled) return ok();
+    }
     if (pl.need > kStaticScratchBytes) {
         return fmt("gemm_q4_mlx_tensorops_noalloc: m = %u rows of %u columns need %zu bytes of scratch but the "
                    "built-in scratch holds %zu; use gemm_q4_mlx_tensorops, which allocates",

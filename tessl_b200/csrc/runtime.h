@@ -218,6 +218,8 @@ uint32_t gemm_q4_mlx_tensorops_max_k(uint32_t m, uint32_t n, uint32_t group_size
 Result gemm_q4_mlx_tensorops(TesslRuntime *rt, const TesslQ4MlxBank &bank, const TesslBuf &x_bf16,
                              const TesslBuf &y, const TesslQuantShape &shape, uint32_t m, OutKind out);
 Result peer_gather(TesslRuntime *rt, const TesslPeerGather &gather);
+Result prefill_as_small_batches(TesslRuntime *rt, const TesslQ4MlxBank &bank, const TesslBuf &x_bf16, const TesslBuf &y,
+                                const TesslQuantShape &shape, uint32_t m, OutKind out, bool *handled);
 Result q8_mlx_mma(TesslRuntime *rt, const TesslBuf &codes, const TesslBuf &sb, const TesslBuf &x_bf16, const TesslBuf &y,
                   uint32_t rows, uint32_t cols, uint32_t group_size, uint32_t m, OutKind out, bool *handled);
 Result gemm_q4_mlx_tensorops_noalloc(TesslRuntime *rt, const TesslQ4MlxBank &bank, const TesslBuf &x_bf16,
