@@ -410,6 +410,10 @@ def measure_sharded_lm_head(ctx, args, world, rank):
             peer = sharded.PeerGather(per * 2)
         except Exception:  # noqa: BLE001
             peer = None
+        agreed = torch.tensor([1 if peer is not None else 0], device=ctx["dev"])
+        dist.all_reduce(agreed, op=dist.ReduceOp.MIN)  # all ranks take the same exchange
+        if int(agreed.item()) == 0:
+            peer = None
     if peer is not None:
         y_local, y_full = peer.local(torch.bfloat16), peer.full(torch.bfloat16)
     else:
@@ -713,23 +717,51 @@ def main():
             line["extra"] = measure_extra(ctx, args)
         line["cpu_baseline"] = cpu_baseline(args)
     else:
-        # every rank copies its activations in and reads its result out; the slowest rank's time counts
-        e2e = measure_e2e(ctx, args)
-        torch = ctx["torch"]
-        t = torch.tensor([e2e["ms_per_step"], e2e["ms_per_step_synchronous"]], device=ctx["dev"], dtype=torch.float64)
-        ctx["dist"].all_reduce(t, op=ctx["dist"].ReduceOp.MAX)
-        e2e["ms_per_step"], e2e["ms_per_step_synchronous"] = float(t[0].item()), float(t[1].item())
-        e2e["value"] = STEP_WEIGHT_BYTES / (e2e["ms_per_step"] * 1e-3) / 1e9
-        e2e["value_every_call_synchronous"] = STEP_WEIGHT_BYTES / (e2e["ms_per_step_synchronous"] * 1e-3) / 1e9
-        e2e["how"] += f"; on each of the {world} ranks, slowest rank's time"
-        line["e2e"] = e2e
-        sharded_head = measure_sharded_lm_head(ctx, args, world, rank)
-        line["extra"] = {f"lm_head 151936x4096 m=1 sharded over {world} GPUs": sharded_head}
+        # The headline figure is complete here. The two secondary measurements below and the closing
+        # barrier involve further collectives; if one of them stalls or fails on some rank, the line is
+        # still printed once (with the reason in place of the missing figure) and every rank leaves
+        # without waiting for the others.
+        emit = threading.Lock()
+        printed = [False]
+
+        def print_line():
+            with emit:
+                if rank == 0 and not printed[0]:
+                    print(json.dumps(line), flush=True)
+                printed[0] = True
+
+        def leave(reason: str):
+            if not printed[0]:
+                line.setdefault("extra", {})["incomplete"] = reason
+            print_line()
+            sys.stdout.flush()
+            os._exit(0)
+
+        watchdog = threading.Timer(120.0, leave, args=("secondary measurements did not finish within 120 s",))
+        watchdog.daemon = True
+        watchdog.start()
+        try:
+            # every rank copies its activations in and reads its result out; the slowest rank's time counts
+            e2e = measure_e2e(ctx, args)
+            torch = ctx["torch"]
+            t = torch.tensor([e2e["ms_per_step"], e2e["ms_per_step_synchronous"]], device=ctx["dev"], dtype=torch.float64)
+            ctx["dist"].all_reduce(t, op=ctx["dist"].ReduceOp.MAX)
+            e2e["ms_per_step"], e2e["ms_per_step_synchronous"] = float(t[0].item()), float(t[1].item())
+            e2e["value"] = STEP_WEIGHT_BYTES / (e2e["ms_per_step"] * 1e-3) / 1e9
+            e2e["value_every_call_synchronous"] = STEP_WEIGHT_BYTES / (e2e["ms_per_step_synchronous"] * 1e-3) / 1e9
+            e2e["how"] += f"; on each of the {world} ranks, slowest rank's time"
+            line["e2e"] = e2e
+            sharded_head = measure_sharded_lm_head(ctx, args, world, rank)
+            line["extra"] = {f"lm_head 151936x4096 m=1 sharded over {world} GPUs": sharded_head}
+        except Exception as e:  # noqa: BLE001
+            leave(f"{type(e).__name__}: {e}")
+        print_line()
+        ctx["dist"].barrier()
+        watchdog.cancel()
+        ctx["dist"].destroy_process_group()
+        return
     if rank == 0:
         print(json.dumps(line), flush=True)
-    if world > 1:
-        ctx["dist"].barrier()
-        ctx["dist"].destroy_process_group()
 
 
 if __name__ == "__main__":
