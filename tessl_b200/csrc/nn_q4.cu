@@ -224,8 +224,15 @@ bool mma_ok(const Q4GemvParams &p)
     return true;
 }
 
+/// A launch over a window of `cols` columns of longer rows (one K chunk): distances in global
+/// memory between packed rows and scale/bias rows (bytes) and between batch rows of x (elements).
+/// Zeros: dense rows.
+struct MmaWindow {
+    uint32_t row_pitch = 0, sb_pitch = 0, x_pitch = 0;
+};
+
 template <int SW, int WPG, int NB, bool BATCH, bool Q8 = false>
-Result launch_mma_one(TesslRuntime *rt, const Q4GemvParams &p, int m)
+Result launch_mma_one(TesslRuntime *rt, const Q4GemvParams &p, int m, const MmaWindow &w = MmaWindow{})
 {
     auto kernel = q4m::q4_gemv_mma_kernel<SW, WPG, NB, BATCH, Q8>;
     constexpr uint32_t RPB = 16 / NB;
@@ -240,6 +247,9 @@ Result launch_mma_one(TesslRuntime *rt, const Q4GemvParams &p, int m)
     mp.nseg = p.nseg, mp.total_rb = rb;
     mp.x = p.x, mp.m = (uint32_t)m, mp.cols = p.cols, mp.group_shift = p.group_shift;
     mp.epi = p.epi, mp.out_bf16 = p.out_bf16;
+    mp.row_pitch = w.row_pitch ? w.row_pitch : p.cols >> 1;
+    mp.sb_pitch = w.sb_pitch ? w.sb_pitch : (p.cols >> p.group_shift) * 4;
+    mp.x_pitch = w.x_pitch ? w.x_pitch : (Q8 ? p.cols >> 1 : p.cols);
     mp.status = rt->status_dev;
 #ifdef TESSL_GEMV_TIMING
     mp.timing = nullptr;
@@ -290,28 +300,55 @@ Result launch_mma_one(TesslRuntime *rt, const Q4GemvParams &p, int m)
 }
 
 template <int SW, int WPG>
-Result launch_mma_sw(TesslRuntime *rt, const Q4GemvParams &p, int m, int nb)
+Result launch_mma_sw(TesslRuntime *rt, const Q4GemvParams &p, int m, int nb, const MmaWindow &w)
 {
-    if (nb == 2) return launch_mma_one<SW, WPG, 2, false>(rt, p, m);
-    if (m == 1) return launch_mma_one<SW, WPG, 1, false>(rt, p, m);
-    return launch_mma_one<SW, WPG, 1, true>(rt, p, m);
+    if (nb == 2) return launch_mma_one<SW, WPG, 2, false>(rt, p, m, w);
+    if (m == 1) return launch_mma_one<SW, WPG, 1, false>(rt, p, m, w);
+    return launch_mma_one<SW, WPG, 1, true>(rt, p, m, w);
 }
 
-Result launch_mma(TesslRuntime *rt, const Q4GemvParams &p, int m, int nb)
+Result launch_mma(TesslRuntime *rt, const Q4GemvParams &p, int m, int nb, const MmaWindow &w = MmaWindow{})
 {
     const int sw = (int)(p.cols / 512), wpg = 1 << (p.group_shift - 5);
     if (sw == 8) {
-        if (wpg == 1) return launch_mma_sw<8, 1>(rt, p, m, nb);
-        if (wpg == 2) return launch_mma_sw<8, 2>(rt, p, m, nb);
-        return launch_mma_sw<8, 4>(rt, p, m, nb);
+        if (wpg == 1) return launch_mma_sw<8, 1>(rt, p, m, nb, w);
+        if (wpg == 2) return launch_mma_sw<8, 2>(rt, p, m, nb, w);
+        return launch_mma_sw<8, 4>(rt, p, m, nb, w);
     }
     if (sw == 4) {
-        if (wpg == 1) return launch_mma_sw<4, 1>(rt, p, m, nb);
-        if (wpg == 2) return launch_mma_sw<4, 2>(rt, p, m, nb);
-        return launch_mma_sw<4, 4>(rt, p, m, nb);
+        if (wpg == 1) return launch_mma_sw<4, 1>(rt, p, m, nb, w);
+        if (wpg == 2) return launch_mma_sw<4, 2>(rt, p, m, nb, w);
+        return launch_mma_sw<4, 4>(rt, p, m, nb, w);
     }
-    if (wpg == 1) return launch_mma_sw<2, 1>(rt, p, m, nb);
-    return launch_mma_sw<2, 2>(rt, p, m, nb);
+    if (wpg == 1) return launch_mma_sw<2, 1>(rt, p, m, nb, w);
+    return launch_mma_sw<2, 2>(rt, p, m, nb, w);
+}
+
+/// Batches of 3..8 rows over rows longer than the tensor-core kernel's 4096 columns (a 12288-column
+/// down projection in batched decode): one launch of that kernel per window of 4096 columns, each
+/// after the first adding to the f32 result of those before it (the kernel's add-residual epilogue
+/// with the output as the residual; launches on one stream are ordered). The FMA-pipe kernel this
+/// replaces costs one pass per batch row (4096 x 12288: 65 us at M = 8 against 21 us here; at
+/// M = 2 it is still the faster one, 17 us against 20 us). Returns false if the call does not fit.
+bool launch_mma_windows(TesslRuntime *rt, const Q4GemvParams &p, int m, int nb, Result &res)
+{
+    constexpr uint32_t W = 4096;
+    if (m < 3 || m > 8 || nb != 1 || p.nseg != 1 || p.cols <= W || p.cols % W != 0 || p.out_bf16) return false;
+    if (p.epi != q4k::EPI_STORE) return false;  // a residual is added once, after the whole sum: not expressible here
+    Q4GemvParams q = p;
+    q.cols = W;
+    if (!mma_ok(q)) return false;
+    MmaWindow w;
+    w.row_pitch = p.cols >> 1, w.sb_pitch = (p.cols >> p.group_shift) * 4, w.x_pitch = p.cols;
+    for (uint32_t c = 0; c < p.cols / W; ++c) {
+        q.x = p.x + (size_t)c * W;
+        q.seg[0].packed0 = p.seg[0].packed0 + (size_t)c * (W / 2);
+        q.seg[0].sb0 = p.seg[0].sb0 + (size_t)c * (W >> p.group_shift);
+        if (c > 0) q.epi = q4k::EPI_ADD_RESID, q.seg[0].resid = static_cast<const float *>(p.seg[0].out);
+        res = launch_mma(rt, q, m, 1, w);
+        if (!res.empty()) return true;
+    }
+    return true;
 }
 
 template <int SW, int WPG>
@@ -339,6 +376,10 @@ Result launch_q4_gemv(TesslRuntime *rt, Q4GemvParams p, int m, int nb)
 {
     const uint32_t nchunks = std::max<uint32_t>(1u, (p.cols + q4k::kChunk - 1) / q4k::kChunk);
     if (m >= 1 && m <= 8 && (nb == 1 || m == 1) && mma_ok(p)) return launch_mma(rt, p, m, nb);
+    {
+        Result res = ok();
+        if (launch_mma_windows(rt, p, m, nb, res)) return res;
+    }
     if (m == 1 && nchunks <= 4 && tma_ok(p)) {
         if (nb == 1) {
             if (nchunks == 1) return launch_tma<1, 8, 1>(rt, p);

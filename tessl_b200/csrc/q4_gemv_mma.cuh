@@ -82,6 +82,12 @@ struct Params {
     uint32_t stages;
     int epi;
     int out_bf16;
+    // A launch may cover a window of `cols` columns of longer rows (a K chunk): bytes between packed
+    // rows and between scale/bias rows in global memory, elements between the batch rows of x. Dense
+    // rows: cols / 2, (cols >> group_shift) * 4 and cols.
+    uint32_t row_pitch;
+    uint32_t sb_pitch;
+    uint32_t x_pitch;
     uint32_t *status;
 #ifdef TESSL_GEMV_TIMING
     unsigned long long *timing;  // [grid][8] cycles per role and phase (development builds only)
@@ -181,10 +187,13 @@ __global__ void __launch_bounds__(kThreads, TESSL_GEMV_MMA_MIN_BLOCKS) q4_gemv_m
         // instructions per stage: the warp shares its scheduler with consumer warps that
         // saturate it, so every instruction here waits for an issue slot. Lanes 0-15 own
         // the 16 row slots of a stage, lanes 16 (and 17) the scale/bias rows of a bank.
-        const uint32_t my_bank = lane < 16 ? (uint32_t)lane / RPB : (uint32_t)lane - 16;
-        const uint32_t my_r = lane < 16 ? (uint32_t)lane % RPB : 0u;
-        const bool copies = lane < 16 + NB;
-        const uint32_t my_dst = lane < 16 ? (uint32_t)lane * pitch : off_sb + my_bank * RPB * sb_row_bytes;
+        // Windowed rows (NB = 1 only): the scale/bias rows are not contiguous, lanes 16-31 fetch one each.
+        const bool sb_by_row = NB == 1 && p.sb_pitch != sb_row_bytes;
+        const uint32_t my_bank = lane < 16 ? (uint32_t)lane / RPB : (sb_by_row ? 0u : (uint32_t)lane - 16);
+        const uint32_t my_r = lane < 16 ? (uint32_t)lane % RPB : (sb_by_row ? (uint32_t)lane - 16 : 0u);
+        const bool copies = sb_by_row || lane < 16 + NB;
+        const uint32_t my_dst = lane < 16 ? (uint32_t)lane * pitch
+                                          : off_sb + (sb_by_row ? my_r : my_bank * RPB) * sb_row_bytes;
         uint32_t s = 0, ph = 0, issued = 0;
         int cur_seg = -1;
         uint32_t seg_end_rb = 0, seg_rows = 0, row0 = 0;
@@ -203,11 +212,12 @@ __global__ void __launch_bounds__(kThreads, TESSL_GEMV_MMA_MIN_BLOCKS) q4_gemv_m
                 seg_end_rb = sg.rb_begin + (sg.rows + RPB - 1) / RPB;
                 row0 = (rb - sg.rb_begin) * RPB;
                 if (lane < 16) {
-                    src = (my_bank == 0 ? sg.packed0 : sg.packed1) + (size_t)(row0 + my_r) * row_bytes;
-                    src_step = RPB * row_bytes;
+                    src = (my_bank == 0 ? sg.packed0 : sg.packed1) + (size_t)(row0 + my_r) * p.row_pitch;
+                    src_step = RPB * p.row_pitch;
                 } else {
-                    src = reinterpret_cast<const uint8_t *>((my_bank == 0 ? sg.sb0 : sg.sb1)) + (size_t)row0 * sb_row_bytes;
-                    src_step = RPB * sb_row_bytes;
+                    src = reinterpret_cast<const uint8_t *>((my_bank == 0 ? sg.sb0 : sg.sb1)) +
+                          (size_t)(row0 + (sb_by_row ? my_r : 0u)) * p.sb_pitch;
+                    src_step = RPB * p.sb_pitch;
                 }
             }
             if (!mbar_wait(empty(s), ph ^ 1u, abortp, 64)) {
@@ -221,7 +231,11 @@ __global__ void __launch_bounds__(kThreads, TESSL_GEMV_MMA_MIN_BLOCKS) q4_gemv_m
             __syncwarp();
             if (copies) {
                 if (lane >= 16) {
-                    bulk_g2s(st + my_dst, src, nrows * sb_row_bytes, full(s));
+                    if (!sb_by_row) {
+                        bulk_g2s(st + my_dst, src, nrows * sb_row_bytes, full(s));
+                    } else if (my_r < nrows) {
+                        bulk_g2s(st + my_dst, src, sb_row_bytes, full(s));
+                    }
                 } else if (my_r < nrows) {
                     bulk_g2s(st + my_dst, src, row_bytes, full(s));
                 }
@@ -324,7 +338,7 @@ __global__ void __launch_bounds__(kThreads, TESSL_GEMV_MMA_MIN_BLOCKS) q4_gemv_m
         float xs[NGS];  // group sums of the activations: column g (BATCH) or the vector (M = 1)
         {
             const uint32_t n = BATCH ? min(g, p.m - 1) : 0u;
-            const uint16_t *xrow = p.x + (size_t)n * (Q8 ? K / 2 : K);
+            const uint16_t *xrow = p.x + (size_t)n * p.x_pitch;
 #pragma unroll
             for (int jj = 0; jj < NGS; ++jj) {
                 float part = 0.0f;

@@ -168,7 +168,10 @@ def test_small_m_gemm_matches_the_oracle(rt, rows, cols, group, m):
 
 TENSOR_GEMV_SHAPES = [(40, 1024, 32), (257, 1024, 64), (40, 2048, 32), (257, 2048, 64), (72, 2048, 128),
                       (40, 4096, 32), (129, 4096, 64), (257, 4096, 128),
-                      (40, 8192, 64), (257, 12288, 64)]  # longer rows: the FMA-pipe kernels, same contract
+                      # longer rows: M = 1 on the FMA-pipe kernels, batches as windows of 4096 columns on
+                      # the MMA kernel, each launch adding to the ones before it; same contract
+                      (40, 8192, 64), (257, 12288, 64), (72, 8192, 128), (33, 16384, 32),
+                      (40, 6144, 64)]  # not a multiple of 4096: FMA-pipe kernels for every M
 
 
 @pytest.mark.parametrize("rows,cols,group", TENSOR_GEMV_SHAPES)

@@ -61,8 +61,10 @@ def test_noalloc_entry_refuses_what_does_not_fit_and_keeps_the_other_refusals(rt
     bank, x, shape = _case(rt, 0x7E550440, 8, 64, 4096, 64)
     y = rt.alloc_buffer(8 * 64 * 4)
     rt.take_dispatch_count()
-    big = nn.GpuBuffer(x.ptr, 2000 * 4096 * 2)  # a capacity claim only: the call is refused before any access
-    ybig = nn.GpuBuffer(y.ptr, 2000 * 64 * 4)
+    # real (never touched) buffers of the claimed sizes: capacity claims laid over the small ones could
+    # overlap each other, depending on where the allocator put them, and trip the aliasing refusal first
+    big = rt.alloc_buffer(2000 * 4096 * 2)
+    ybig = rt.alloc_buffer(2000 * 64 * 4)
     with pytest.raises(nn.TesslError, match="built-in scratch holds 8388608"):
         nn.gemm_q4_mlx_tensorops_noalloc(rt, bank, big, ybig, shape, 2000)
     with pytest.raises(nn.TesslError, match="group_size 256"):
