@@ -125,6 +125,26 @@ TESSL_API int32_t tessl_runtime_device(TesslRuntime *rt);
  * `poison_as_shared_event_timeout_for_test`, src/runtime.rs:1076). */
 TESSL_API int32_t tessl_runtime_poison_for_test(TesslRuntime *rt);
 
+/* Prefill GEMM tile choice, for tuning runs and for tests that must reach every
+ * compiled tile: tile_n in {128, 192, 256} forces the tile width of later
+ * tessl_gemm_q4_mlx_tensorops* calls on this runtime (0 = the library's own
+ * estimate), pair = 1 / 0 forces the two-CTA or the single-CTA kernel (-1 = the
+ * library decides). tessl_runtime_last_prefill_tile reports what the most
+ * recent prefill call launched (tile_n = 0 if it ran no tile kernel). No
+ * counterpart in the reference, whose kernel has one 32 x 32 tile. */
+TESSL_API int32_t tessl_runtime_set_prefill_tile(TesslRuntime *rt, uint32_t tile_n, int32_t pair, char *err, size_t err_len);
+TESSL_API int32_t tessl_runtime_last_prefill_tile(TesslRuntime *rt, uint32_t *tile_n, uint32_t *pair, char *err,
+                                        size_t err_len);
+
+/* Clock budget (SM clocks) of the bounded waits a kernel of this runtime makes
+ * on another GPU's flags (tessl_peer_gather and the sharded GEMV's exchange);
+ * 0 restores the default of about half a second. A wait that runs out makes the
+ * kernel write a status word and return; the next wait on the host reports it
+ * and poisons the runtime, the way the reference reports a shared-event
+ * timeout (src/runtime.rs:1498-1531). A test uses a small budget to exercise
+ * that path without sitting through the default one. */
+TESSL_API int32_t tessl_runtime_set_peer_wait_limit(TesslRuntime *rt, uint64_t clocks, char *err, size_t err_len);
+
 /* Device buffers (`GpuRuntime::alloc_buffer`, `GpuBuffer::write_bytes`,
  * `read_*`; src/runtime.rs:2083, src/tensor.rs). Copies are ordered on the
  * runtime's stream and complete before return. */
@@ -215,8 +235,9 @@ TESSL_API int32_t tessl_gemm_q4_mlx_tensorops_bf16(TesslRuntime *rt, TesslQ4MlxB
  * It has no counterpart in the reference. The regular entry keeps its
  * intermediate data (an f16 copy of X with per-group sums, and one scale per
  * row) in a buffer it grows with cudaMalloc; a serving loop that forbids
- * allocation in steady state, code living under another framework's allocator,
- * or a thread that is capturing its stream cannot afford that call. This entry
+ * allocation in steady state (cudaMalloc can synchronise the device and can fail
+ * when memory is tight) or code living under another framework's allocator
+ * cannot afford that call. This entry
  * uses a fixed 8 MiB array inside the library instead (held by every GPU that
  * loads the library until the process exits) and refuses, with a message that
  * names the sizes, any call whose m * K_aug * 2 + m * 4 bytes do not fit

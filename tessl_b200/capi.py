@@ -66,6 +66,9 @@ SIGNATURES = {
     "tessl_runtime_stream": (C.c_void_p, [_RT]),
     "tessl_runtime_device": (C.c_int32, [_RT]),
     "tessl_runtime_poison_for_test": (C.c_int32, [_RT]),
+    "tessl_runtime_set_prefill_tile": (C.c_int32, [_RT, _u32, C.c_int32] + _ERR),
+    "tessl_runtime_last_prefill_tile": (C.c_int32, [_RT, C.POINTER(_u32), C.POINTER(_u32)] + _ERR),
+    "tessl_runtime_set_peer_wait_limit": (C.c_int32, [_RT, C.c_uint64] + _ERR),
     "tessl_buffer_alloc": (C.c_int32, [_RT, C.c_uint64, C.POINTER(Buf)] + _ERR),
     "tessl_buffer_free": (C.c_int32, [_RT, Buf] + _ERR),
     "tessl_buffer_write": (C.c_int32, [_RT, Buf, C.c_uint64, C.c_void_p, C.c_uint64] + _ERR),

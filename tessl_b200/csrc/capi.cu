@@ -244,6 +244,39 @@ int32_t tessl_runtime_poison_for_test(TesslRuntime *rt)
     return TESSL_OK;
 }
 
+int32_t tessl_runtime_set_prefill_tile(TesslRuntime *rt, uint32_t tile_n, int32_t pair, char *err, size_t err_len)
+{
+    if (refuse_unowned(rt, err, err_len)) return TESSL_ERR;
+    if ((tile_n != 0 && tile_n != 128 && tile_n != 192 && tile_n != 256) || pair < -1 || pair > 1) {
+        write_err(err, err_len,
+                  tessl::fmt("tessl_runtime_set_prefill_tile: tile_n %u is not one of [0, 128, 192, 256] or pair %d is "
+                             "not one of [-1, 0, 1]", tile_n, pair));
+        return TESSL_ERR;
+    }
+    rt->prefill_force_bn = (int)tile_n;
+    rt->prefill_force_pair = pair;
+    return TESSL_OK;
+}
+
+int32_t tessl_runtime_last_prefill_tile(TesslRuntime *rt, uint32_t *tile_n, uint32_t *pair, char *err, size_t err_len)
+{
+    if (refuse_unowned(rt, err, err_len)) return TESSL_ERR;
+    if (!tile_n || !pair) {
+        write_err(err, err_len, "tessl_runtime_last_prefill_tile: null out");
+        return TESSL_ERR;
+    }
+    *tile_n = (uint32_t)rt->prefill_last_bn;
+    *pair = (uint32_t)rt->prefill_last_pair;
+    return TESSL_OK;
+}
+
+int32_t tessl_runtime_set_peer_wait_limit(TesslRuntime *rt, uint64_t clocks, char *err, size_t err_len)
+{
+    if (refuse_unowned(rt, err, err_len)) return TESSL_ERR;
+    rt->peer_wait_clocks = clocks;
+    return TESSL_OK;
+}
+
 int32_t tessl_buffer_alloc(TesslRuntime *rt, uint64_t nbytes, TesslBuf *out, char *err, size_t err_len)
 {
     return guarded(rt, err, err_len, false, [&]() -> Result {

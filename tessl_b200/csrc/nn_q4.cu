@@ -169,10 +169,6 @@ Result launch_tma(TesslRuntime *rt, const Q4GemvParams &p)
     tp.nseg = p.nseg, tp.total_rb = rb;
     tp.x = p.x, tp.cols = p.cols, tp.group_shift = p.group_shift, tp.epi = p.epi, tp.out_bf16 = p.out_bf16;
     tp.status = rt->status_dev;
-#ifdef TESSL_GEMV_TIMING
-    tp.timing = nullptr;
-    if (const char *e = std::getenv("TESSL_B200_TIMING_PTR")) tp.timing = (unsigned long long *)std::strtoull(e, nullptr, 0);
-#endif
     const uint32_t stage_bytes = NB * RS * ((p.cols >> 1) + (p.cols >> p.group_shift) * 4);
     const uint32_t warps = (uint32_t)cfg.consumers;
     const uint32_t stages = std::max<uint32_t>(1u, (uint32_t)cfg.ring_kib * 1024u / (stage_bytes * warps));
@@ -251,10 +247,6 @@ Result launch_mma_one(TesslRuntime *rt, const Q4GemvParams &p, int m, const MmaW
     mp.sb_pitch = w.sb_pitch ? w.sb_pitch : (p.cols >> p.group_shift) * 4;
     mp.x_pitch = w.x_pitch ? w.x_pitch : (Q8 ? p.cols >> 1 : p.cols);
     mp.status = rt->status_dev;
-#ifdef TESSL_GEMV_TIMING
-    mp.timing = nullptr;
-    if (const char *e = std::getenv("TESSL_B200_TIMING_PTR")) mp.timing = (unsigned long long *)std::strtoull(e, nullptr, 0);
-#endif
     const uint32_t gpr = p.cols >> p.group_shift;
     const uint32_t part = BATCH ? q4m::kConsumers * 16 * 8 * 4 : q4m::kConsumers * 16 * 4;
     const uint32_t stage_bytes = 16 * ((p.cols >> 1) + q4m::kRowPad) + 16 * gpr * 4 + part;

@@ -36,24 +36,8 @@ struct GemmParams {
     uint32_t tiles_m, tiles_n;
     int out_bf16;
     uint32_t *status;
-#ifdef TESSL_GEMM_TIMING
-    long long *timing;  // [grid][32] cycles per role and phase (development builds only)
-#endif
 };
 
-#ifdef TESSL_GEMM_TIMING
-// Development builds: TSTAMP(i) adds the cycles since the previous stamp of this thread to slot i.
-#define TSTAMP(i)                          \
-    do {                                   \
-        const long long _now = clock64();  \
-        tacc[i] += _now - tlast;           \
-        tlast = _now;                      \
-    } while (0)
-#else
-#define TSTAMP(i) \
-    do {          \
-    } while (0)
-#endif
 
 // ---------------------------------------------------------------- PTX wrappers ---
 

@@ -420,12 +420,7 @@ Result launch_gemm(TesslRuntime *rt, const CUtensorMap &ma, const CUtensorMap &m
 {
     using C = Cfg<BN>;
     auto kernel = q4_prefill_gemm_kernel<BN>;
-    static bool opted = false;
-    if (!opted) {
-        TESSL_TRY(cuda_check(rt, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM),
-                             "gemm_q4_mlx_tensorops: shared memory opt-in"));
-        opted = true;
-    }
+    TESSL_TRY(smem_opt_in(rt, reinterpret_cast<const void *>(kernel), C::SMEM, "gemm_q4_mlx_tensorops: shared memory opt-in"));
     const uint32_t tiles = p.tiles_m * p.tiles_n;
     const uint32_t grid = std::min<uint32_t>(tiles, (uint32_t)rt->sm_count);
     kernel<<<grid, C::THREADS, C::SMEM, rt->stream>>>(ma, mw, p);
@@ -439,12 +434,7 @@ Result launch_gemm_pair(TesslRuntime *rt, const CUtensorMap &ma, const CUtensorM
 {
     using C = PairCfg<BN>;
     auto kernel = q4_prefill_gemm_pair_kernel<BN>;
-    static bool opted = false;
-    if (!opted) {
-        TESSL_TRY(cuda_check(rt, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::SMEM),
-                             "gemm_q4_mlx_tensorops: shared memory opt-in"));
-        opted = true;
-    }
+    TESSL_TRY(smem_opt_in(rt, reinterpret_cast<const void *>(kernel), C::SMEM, "gemm_q4_mlx_tensorops: shared memory opt-in"));
     const uint32_t tiles = p.tiles_m * p.tiles_n;
     const uint32_t clusters = std::min<uint32_t>(tiles, (uint32_t)rt->sm_count / 2);
     kernel<<<2 * clusters, C::THREADS, C::SMEM, rt->stream>>>(ma, mw, p);
@@ -509,20 +499,11 @@ Result prefill_validate(const TesslQ4MlxBank &bank, const TesslBuf &x_bf16, cons
 /// The pair kernel's 256-row tile is half padding for m <= 128, but each CTA still expands only half of
 /// the weight rows and it has the better pipeline: measured 34.6 us against the single-CTA kernel's 48.9 us
 /// at m = 16 .. 64, N = 12288, K = 4096. So the pair kernel runs for every m; the single-CTA kernel is
-/// what TESSL_B200_PREFILL_PAIR=0 (or a GPU with one SM) selects.
-constexpr uint32_t kPairMinRows = 1;
+/// what a GPU with one SM, or `tessl_runtime_set_prefill_tile(rt, bn, 0)`, selects.
 
 /// Tile width with the least estimated time: waves of tiles x the cost of one tile's K block.
 int pick_tile_width(uint64_t tiles_m, uint32_t n, uint32_t slots)
 {
-    // TESSL_B200_PREFILL_BN = 128 | 192 | 256 forces a width (for tuning runs).
-    static int forced = -1;
-    if (forced < 0) {
-        const char *e = std::getenv("TESSL_B200_PREFILL_BN");
-        const int v = e ? std::atoi(e) : 0;
-        forced = (v == 128 || v == 192 || v == 256) ? v : 0;
-    }
-    if (forced) return forced;
     int best_bn = 256;
     uint64_t best_cost = ~0ull;
     for (int bn : {256, 192, 128}) {
@@ -533,19 +514,6 @@ int pick_tile_width(uint64_t tiles_m, uint32_t n, uint32_t slots)
         if (cost < best_cost) best_cost = cost, best_bn = bn;
     }
     return best_bn;
-}
-
-/// Rows of X from which the CTA-pair kernel is used: TESSL_B200_PREFILL_PAIR = 0 never,
-/// = n > 0 for m >= n; default below.
-uint32_t pair_min_rows()
-{
-    static int64_t v = -1;
-    if (v < 0) {
-        const char *e = std::getenv("TESSL_B200_PREFILL_PAIR");
-        v = e ? std::atoll(e) : (int64_t)kPairMinRows;
-        if (e && v <= 0) v = 0xffffffffll;
-    }
-    return (uint32_t)v;
 }
 
 /// Pre-pass and GEMM of a validated call; `scratch` holds `plan.need` bytes.
@@ -559,9 +527,12 @@ Result prefill_launch(TesslRuntime *rt, const TesslQ4MlxBank &bank, const TesslB
     rt->dispatch_count += 1;
     TESSL_TRY(cuda_check(rt, cudaGetLastError(), "gemm_q4_mlx_tensorops pre-pass launch"));
 
-    const bool pair = m >= pair_min_rows() && rt->sm_count >= 2;
+    const bool pair = rt->sm_count >= 2 && rt->prefill_force_pair != 0;
     const uint32_t tiles_m = pair ? (m + 2 * BM - 1) / (2 * BM) : (m + BM - 1) / BM;
-    const int bn = pick_tile_width(tiles_m, pl.n, pair ? (uint32_t)rt->sm_count / 2 : (uint32_t)rt->sm_count);
+    const int bn = rt->prefill_force_bn
+                       ? rt->prefill_force_bn
+                       : pick_tile_width(tiles_m, pl.n, pair ? (uint32_t)rt->sm_count / 2 : (uint32_t)rt->sm_count);
+    rt->prefill_last_bn = bn, rt->prefill_last_pair = pair ? 1 : 0;
 
     EncodeTiled enc = nullptr;
     TESSL_TRY(tensormap_encoder(rt, &enc));
@@ -583,10 +554,6 @@ Result prefill_launch(TesslRuntime *rt, const TesslQ4MlxBank &bank, const TesslB
     p.tiles_n = (pl.n + bn - 1) / bn;
     p.out_bf16 = out == OUT_BF16;
     p.status = rt->status_dev;
-#ifdef TESSL_GEMM_TIMING
-    p.timing = nullptr;
-    if (const char *e = std::getenv("TESSL_B200_TIMING_PTR")) p.timing = (long long *)std::strtoull(e, nullptr, 0);
-#endif
     if (pair) {
         if (bn == 256) return launch_gemm_pair<256>(rt, ma, mw, p);
         if (bn == 192) return launch_gemm_pair<192>(rt, ma, mw, p);
@@ -598,7 +565,7 @@ Result prefill_launch(TesslRuntime *rt, const TesslQ4MlxBank &bank, const TesslB
 }
 
 /// Upper bound of the built-in scratch: enough for m * K_aug f16 activations plus
-/// m row scales, e.g. 512 rows at K = 4096, G = 64, or 2048 rows at K = 1024.
+/// m row scales, e.g. 963 rows at K = 4096, G = 64, or 3847 rows at K = 1024.
 constexpr size_t kStaticScratchBytes = size_t(8) << 20;
 
 /// The scratch itself lives in the library image: every GPU that loads the
@@ -648,7 +615,8 @@ Result gemm_q4_mlx_tensorops(TesslRuntime *rt, const TesslQ4MlxBank &bank, const
     bool empty = false;
     TESSL_TRY(prefill_validate(bank, x_bf16, y, shape, m, out, &pl, &empty));
     if (empty) return ok();
-    {
+    rt->prefill_last_bn = 0, rt->prefill_last_pair = 0;
+    if (rt->prefill_force_bn == 0 && rt->prefill_force_pair < 0) {
         bool handled = false;  // a few rows: batches of 8 on the tensor-core GEMV kernel
         TESSL_TRY(prefill_as_small_batches(rt, bank, x_bf16, y, shape, m, out, &handled));
         if (handled) return ok();
@@ -661,9 +629,8 @@ Result gemm_q4_mlx_tensorops(TesslRuntime *rt, const TesslQ4MlxBank &bank, const
 
 /// `gemm_q4_mlx_tensorops` for callers that must not allocate device memory
 /// while they run: serving loops that forbid anything that can synchronise the
-/// device or fail for lack of memory in steady state, code inside another
-/// framework's allocator discipline, or a thread that is capturing a stream
-/// (where cudaMalloc is an error). The regular entry grows a scratch buffer
+/// device or fail for lack of memory in steady state, or code inside another
+/// framework's allocator discipline. The regular entry grows a scratch buffer
 /// with cudaMalloc whenever a call needs more than any earlier one; this one
 /// puts the same intermediate data (the f16 copy of X with its group sums, and
 /// the row scales) into a fixed array inside the library and refuses shapes
@@ -682,7 +649,8 @@ Result gemm_q4_mlx_tensorops_noalloc(TesslRuntime *rt, const TesslQ4MlxBank &ban
     bool empty = false;
     TESSL_TRY(prefill_validate(bank, x_bf16, y, shape, m, out, &pl, &empty));
     if (empty) return ok();
-    {
+    rt->prefill_last_bn = 0, rt->prefill_last_pair = 0;
+    if (rt->prefill_force_bn == 0 && rt->prefill_force_pair < 0) {
         bool handled = false;  // needs no scratch at all
         TESSL_TRY(prefill_as_small_batches(rt, bank, x_bf16, y, shape, m, out, &handled));
         if (handled) return ok();

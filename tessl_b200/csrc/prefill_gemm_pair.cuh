@@ -114,11 +114,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PairCfg<BN>::THREADS
         *abortp = 1;
         *(volatile uint32_t *)p.status = (role << 24) | (rank << 23) | (where & 0x7fffffu);
     };
-#ifdef TESSL_GEMM_TIMING
-    long long tacc[6] = {0, 0, 0, 0, 0, 0};
-    const long long tstart = clock64();
-    long long tlast = tstart;
-#endif
 
     if (warp == 0) {
         // ------------------------------------------------ TMA producer: X tiles ---
@@ -133,13 +128,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PairCfg<BN>::THREADS
                         ok_ = false;
                         break;
                     }
-                    TSTAMP(0);  // wait empty
                     // The leader expects both CTAs' tiles on its barrier; either CTA's bytes may land first.
                     if (rank == 0) mbar_expect_tx(full(ring.stage), 2 * C::A_BYTES);
                     tma_load_2d_pair(base + C::OFF_A + ring.stage * C::A_BYTES, &map_a, (int)(kb * BK), m0,
                                      full(ring.stage) + lead_delta);
                     ring.advance();
-                    TSTAMP(1);  // issue A
                 }
             }
             // These copies are covered by the leader's wait for its last MMA, which has read them all.
@@ -158,12 +151,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PairCfg<BN>::THREADS
                         ok_ = false;
                         break;
                     }
-                    TSTAMP(0);  // wait q_empty
                     mbar_expect_tx(q_full(ring.stage), C::Q_BYTES);
                     tma_load_2d(base + C::OFF_Q + ring.stage * C::Q_BYTES, &map_w, (int)(kb * 32), n0, q_full(ring.stage));
                     ring.advance();
                     ++issued;
-                    TSTAMP(1);  // issue Q
                 }
             }
             // Let every copy this thread issued land before the CTA may exit.
@@ -194,7 +185,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PairCfg<BN>::THREADS
                     break;
                 }
                 tcgen05_fence_after();
-                TSTAMP(0);  // wait acc_empty
                 const uint32_t d = tmem_base + buf * 256u;
                 for (uint32_t kb = 0; kb < nkb; ++kb) {
                     if (!mbar_wait(full(ring.stage), ring.phase, abortp)) {
@@ -202,7 +192,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PairCfg<BN>::THREADS
                         ok_ = false;
                         break;
                     }
-                    TSTAMP(1);  // wait full
                     tcgen05_fence_after();
                     const uint32_t a_lo = a_lo0 + ring.stage * (C::A_BYTES >> 4);
                     const uint32_t b_lo = b_lo0 + ring.stage * (C::B_BYTES >> 4);
@@ -211,7 +200,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PairCfg<BN>::THREADS
                     for (uint32_t k4 = 1; k4 < 4; ++k4) tcgen05_mma_f16_pair_elect(d, a_lo + 2 * k4, b_lo + 2 * k4, idesc, 1u);
                     tcgen05_commit_pair_elect(empty(ring.stage));  // both CTAs' A and B stages are free once these MMAs have read them
                     ring.advance();
-                    TSTAMP(2);  // issue MMAs and commit
                 }
                 if (ok_) tcgen05_commit_pair_elect(acc_full(buf));
             }
@@ -235,7 +223,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PairCfg<BN>::THREADS
                 break;
             }
             tcgen05_fence_after();
-            TSTAMP(0);  // wait acc_full
             const uint32_t m_base = ((t % p.tiles_m) * 2 + rank) * BM + quarter * 32;
             const uint32_t n0 = (t / p.tiles_m) * BN;
             const float rs = m_base + lane < p.M ? p.row_scale[m_base + lane] : 0.0f;
@@ -250,7 +237,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PairCfg<BN>::THREADS
             tcgen05_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(acc_empty(buf) + lead_delta);
-            TSTAMP(1);  // drain the accumulator
         }
     } else {
         // ------------------------------------------------ dequant warps ---
@@ -282,7 +268,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PairCfg<BN>::THREADS
                     ok_ = false;
                     break;
                 }
-                TSTAMP(0);  // wait empty
                 const uint32_t brow = b_off + ring.stage * C::B_BYTES;
                 if (kb < p.nkb_main) {
                     if (!mbar_wait(q_full(qring.stage), qring.phase, abortp, C::POLL_DEQUANT)) {
@@ -290,42 +275,26 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PairCfg<BN>::THREADS
                         ok_ = false;
                         break;
                     }
-                    TSTAMP(1);  // wait q_full
                     const uint4 w = lds128(q_off + qring.stage * C::Q_BYTES);
                     __syncwarp();
                     if (lane == 0) mbar_arrive(q_empty(qring.stage));  // the packed stage may be refilled
                     qring.advance(C::NG);
-                    TSTAMP(2);  // read the packed half row
                     const uint32_t words[4] = {w.x, w.y, w.z, w.w};
                     expand_q4_words<4>(words, scale_h2(cur), brow, swz, 4 * h);
                 } else {
                     expand_extra_chunks<4>(sbrow, kb - p.nkb_main, p.gpr, brow, swz, 4 * h);
                 }
-                TSTAMP(3);  // expand and store
                 // generic-proxy stores -> visible to the tensor cores' async-proxy reads
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                TSTAMP(4);  // proxy fence
                 __syncwarp();
                 if (lane == 0) mbar_arrive_cluster(full(ring.stage) + lead_delta);
                 ring.advance(C::NG);
                 cur = nxt;
                 if (kb + 2 * C::NG < p.nkb_main) nxt = scale_word(kb + 2 * C::NG);
-                TSTAMP(5);  // hand over, prefetch
             }
         }
     }
 
-#ifdef TESSL_GEMM_TIMING
-    if (p.timing && lane == 0) {
-        // rows of 8 slots: 0 X producer, 1 MMA issuer, 2 epilogue warp 4, 3 first dequant warp; slot 7 = role's total
-        const int role = warp == 0 ? 0 : warp == 1 ? 1 : warp == 4 ? 2 : warp == C::FIRST_DW ? 3 : -1;
-        if (role >= 0) {
-            long long *o = p.timing + (size_t)blockIdx.x * 32 + role * 8;
-            for (int i = 0; i < 6; ++i) o[i] = tacc[i];
-            o[7] = clock64() - tstart;
-        }
-    }
-#endif
     // Neither CTA may leave, or give up its TMEM, while the other can still signal
     // its barriers or the pair's MMAs can still read its shared memory.
     tcgen05_fence_before();

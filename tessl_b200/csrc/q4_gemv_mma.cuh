@@ -89,23 +89,8 @@ struct Params {
     uint32_t sb_pitch;
     uint32_t x_pitch;
     uint32_t *status;
-#ifdef TESSL_GEMV_TIMING
-    unsigned long long *timing;  // [grid][8] cycles per role and phase (development builds only)
-#endif
 };
 
-#ifdef TESSL_GEMV_TIMING
-#define MMA_TSTAMP(i)                      \
-    do {                                   \
-        const long long _now = clock64();  \
-        tacc[i] += _now - tlast;           \
-        tlast = _now;                      \
-    } while (0)
-#else
-#define MMA_TSTAMP(i) \
-    do {              \
-    } while (0)
-#endif
 
 __device__ __forceinline__ uint2 lds64(uint32_t addr)
 {
@@ -166,11 +151,6 @@ __global__ void __launch_bounds__(kThreads, TESSL_GEMV_MMA_MIN_BLOCKS) q4_gemv_m
         *abortp = 1;
         *(volatile uint32_t *)p.status = (0x40u << 24) | (role << 20) | (where & 0xfffffu);
     };
-#ifdef TESSL_GEMV_TIMING
-    long long tacc[2] = {0, 0};
-    const long long tstart = clock64();
-    long long tlast = tstart;
-#endif
     auto locate = [&](uint32_t rb, Seg &sg, uint32_t &row0) {
         int s = 0;
         if (p.nseg > 1 && rb >= p.seg[1].rb_begin) s = 1;
@@ -224,7 +204,6 @@ __global__ void __launch_bounds__(kThreads, TESSL_GEMV_MMA_MIN_BLOCKS) q4_gemv_m
                 if (lane == 0) fail(1, j);
                 break;
             }
-            MMA_TSTAMP(0);  // wait empty
             const uint32_t nrows = min((uint32_t)RPB, seg_rows - row0);
             const uint32_t st = ring + s * stage_bytes;
             if (lane == 0) mbar_expect_tx(full(s), NB * nrows * (row_bytes + sb_row_bytes));
@@ -243,7 +222,6 @@ __global__ void __launch_bounds__(kThreads, TESSL_GEMV_MMA_MIN_BLOCKS) q4_gemv_m
             src += src_step, row0 += RPB;
             ++issued;
             if (++s == S) s = 0, ph ^= 1u;
-            MMA_TSTAMP(1);  // issue
         }
         // After a timeout elsewhere copies may still be in flight: give the last ring a bounded chance to land.
         if (*abortp && lane == 0) {
@@ -262,7 +240,6 @@ __global__ void __launch_bounds__(kThreads, TESSL_GEMV_MMA_MIN_BLOCKS) q4_gemv_m
                 if (lane == 0) fail(3, j);
                 break;
             }
-            MMA_TSTAMP(0);  // wait done
             Seg sg;
             uint32_t row0;
             locate(rb_lo + j, sg, row0);
@@ -322,7 +299,6 @@ __global__ void __launch_bounds__(kThreads, TESSL_GEMV_MMA_MIN_BLOCKS) q4_gemv_m
             __syncwarp();
             if (lane == 0) mbar_arrive(empty(s));  // partial sums read: the stage may be refilled
             if (++s == S) s = 0, ph ^= 1u;
-            MMA_TSTAMP(1);  // reduce and store
         }
     } else {
         // ------------------------------------------------ consumers ---
@@ -388,16 +364,11 @@ __global__ void __launch_bounds__(kThreads, TESSL_GEMV_MMA_MIN_BLOCKS) q4_gemv_m
         const uint32_t sb_off = (k0 >> p.group_shift) * 4;
 
         uint32_t s = 0, ph = 0;
-#ifdef TESSL_GEMV_TIMING
-        const long long tsetup = clock64() - tstart;
-        tlast = clock64();
-#endif
         for (uint32_t j = 0; j < n_local; ++j) {
             if (!mbar_wait(full(s), ph, abortp, 32)) {  // sleeping between polls leaves issue slots to the producer
                 if (lane == 0) fail(2, j);
                 break;
             }
-            MMA_TSTAMP(0);  // wait full
             const uint32_t st = ring + s * stage_bytes;
             const uint32_t row_lo = st + g * pitch + w_off, row_hi = row_lo + 8 * pitch;
             const uint32_t sb_lo = st + off_sb + g * sb_row_bytes + sb_off, sb_hi = sb_lo + 8 * sb_row_bytes;
@@ -496,21 +467,8 @@ __global__ void __launch_bounds__(kThreads, TESSL_GEMV_MMA_MIN_BLOCKS) q4_gemv_m
             __syncwarp();
             if (lane == 0) mbar_arrive(done(s));  // release: the partial sums are visible to the reducer
             if (++s == S) s = 0, ph ^= 1u;
-            MMA_TSTAMP(1);  // compute
         }
-#ifdef TESSL_GEMV_TIMING
-        if (p.timing && warp == 0 && lane == 0) p.timing[blockIdx.x * 16 + 6] = tsetup;
-#endif
     }
-#ifdef TESSL_GEMV_TIMING
-    if (p.timing && lane == 0 && (warp == 0 || warp >= kConsumers)) {
-        // rows of 2: consumer warp 0, producer, reducer; [6] consumer setup, [7] block total
-        const int role = warp == 0 ? 0 : warp == kConsumers ? 1 : 2;
-        unsigned long long *o = p.timing + blockIdx.x * 16;
-        o[2 * role] = tacc[0], o[2 * role + 1] = tacc[1];
-        if (warp == kConsumers + 1) o[7] = clock64() - tstart;
-    }
-#endif
 }
 
 }  // namespace q4m

@@ -49,9 +49,6 @@ struct TmaParams {
     int epi;
     int out_bf16;
     uint32_t *status;  // runtime status word (pinned host memory), written only on a timeout
-#ifdef TESSL_GEMV_TIMING
-    unsigned long long *timing;  // [grid][4] globaltimer stamps (development builds only)
-#endif
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }

@@ -12,6 +12,7 @@
 
 #include <cstdint>
 #include <cstdio>
+#include <map>
 #include <string>
 #include <thread>
 
@@ -52,6 +53,17 @@ struct TesslRuntime {
     // alias) when a bounded wait inside it gives up. Checked at every wait.
     volatile uint32_t *status_host = nullptr;
     uint32_t *status_dev = nullptr;
+    // Dynamic shared memory already opted in, per kernel. The attribute belongs to the
+    // device's context, so it is remembered per runtime (one device each), not per process.
+    std::map<const void *, size_t> smem_opted;
+    // Prefill GEMM tile choice: what a tuning run or a test asked for (0 / -1 = the library
+    // decides) and what the last call ran (0 = no tile kernel ran, e.g. the small-batch route).
+    int prefill_force_bn = 0;
+    int prefill_force_pair = -1;
+    int prefill_last_bn = 0;
+    int prefill_last_pair = 0;
+    // Clock budget of a bounded device-side wait on another rank (0 = the default).
+    uint64_t peer_wait_clocks = 0;
 };
 
 namespace tessl {
@@ -63,6 +75,23 @@ inline Result cuda_check(TesslRuntime *rt, cudaError_t e, const char *what)
     if (rt) rt->poisoned = true;
     return fmt("%s: CUDA error %d (%s); the runtime is poisoned and must be recreated", what, (int)e,
                cudaGetErrorString(e));
+}
+
+/// Opts `kernel` in to `bytes` of dynamic shared memory on the runtime's device, once per
+/// runtime and size; `carveout` also asks for the largest shared-memory carve-out.
+inline Result smem_opt_in(TesslRuntime *rt, const void *kernel, size_t bytes, const char *what, bool carveout = false)
+{
+    auto it = rt->smem_opted.find(kernel);
+    if (it != rt->smem_opted.end() && it->second >= bytes) return ok();
+    Result r = cuda_check(rt, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes), what);
+    if (!r.empty()) return r;
+    if (carveout) {
+        r = cuda_check(rt, cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                                (int)cudaSharedmemCarveoutMaxShared), what);
+        if (!r.empty()) return r;
+    }
+    rt->smem_opted[kernel] = bytes;
+    return ok();
 }
 
 /// Scratch of at least `bytes`, 256-byte aligned. Growing waits for the stream

@@ -172,6 +172,21 @@ class Runtime:
         capi.call("tessl_runtime_take_dispatch_count", self.handle, C.byref(out))
         return out.value
 
+    def set_prefill_tile(self, tile_n: int = 0, pair: int = -1) -> None:
+        """Force the prefill GEMM's tile width (128 / 192 / 256, 0 = automatic) and kernel
+        (1 = CTA pair, 0 = single CTA, -1 = automatic) for later calls on this runtime."""
+        capi.call("tessl_runtime_set_prefill_tile", self.handle, tile_n, pair)
+
+    def last_prefill_tile(self) -> tuple:
+        """(tile width, pair) the most recent prefill GEMM call launched; (0, 0) if it ran no tile kernel."""
+        bn, pair = C.c_uint32(0), C.c_uint32(0)
+        capi.call("tessl_runtime_last_prefill_tile", self.handle, C.byref(bn), C.byref(pair))
+        return bn.value, pair.value
+
+    def set_peer_wait_limit(self, clocks: int) -> None:
+        """Clock budget of bounded waits on another GPU's flags (0 = the default, about 0.5 s)."""
+        capi.call("tessl_runtime_set_peer_wait_limit", self.handle, clocks)
+
     def alloc_buffer(self, nbytes: int) -> GpuBuffer:
         b = Buf()
         capi.call("tessl_buffer_alloc", self.handle, nbytes, C.byref(b))

@@ -130,6 +130,118 @@ def test_model_shapes_match_the_dequant_matvec(rt, m, n, k, group):
     assert np.array_equal(gb, synth.f32_to_bf16_bits(got.reshape(-1)))
 
 
+def _subset_rows(m):
+    """Rows on either side of every 128-row boundary the tiles have, the first and the last."""
+    rows = {0, m - 1}
+    for b in range(128, m, 128):
+        rows.update((b - 1, b))
+    rows.update(range(7, m, max(1, m // 5)))
+    return np.array(sorted(r for r in rows if 0 <= r < m))
+
+
+def _check_rows_against_the_oracle(got, packed, sb, x, rows, n, k, group, what):
+    """`rows` of the [m, n] result against the dequant-matvec (stated tolerance) and the exact product (gamma_t S)."""
+    xs = np.ascontiguousarray(x.reshape(-1, k)[rows]).reshape(-1)
+    want = api.q4_dense_gemm(packed, sb, xs, len(rows), n, k, group)
+    assert_north_star(got[rows], want, what)
+    assert_gamma_bound(got[rows].reshape(-1), packed, sb, xs, len(rows), n, k, group, extra_terms=group, what=what)
+
+
+def _check_sums_against_the_oracle(got, packed, sb, x, m, n, k, group, what):
+    """Every output takes part: the column sums of Y equal W (sum of the rows of X) and the row sums equal
+    X (sum of the rows of W), both formed in f64 on the host from the bit-exact dequantized weights."""
+    w = api.q4_dequant(packed, sb, n, k, group).astype(np.float64)
+    xf = synth.bf16_bits_to_f32(x).reshape(m, k).astype(np.float64)
+    g64 = got.astype(np.float64)
+    col_want, row_want = w @ xf.sum(axis=0), xf @ w.sum(axis=0)
+    col_tol = 1e-5 * np.abs(g64).sum(axis=0) + 1e-3
+    row_tol = 1e-5 * np.abs(g64).sum(axis=1) + 1e-3
+    bad = np.flatnonzero(np.abs(g64.sum(axis=0) - col_want) > col_tol)
+    assert bad.size == 0, f"{what}: column sums differ at columns {bad[:8]}"
+    bad = np.flatnonzero(np.abs(g64.sum(axis=1) - row_want) > row_tol)
+    assert bad.size == 0, f"{what}: row sums differ at rows {bad[:8]}"
+
+
+@pytest.mark.parametrize("m,n,k,group,tile", [(600, 12251, 256, 32, 256), (600, 12288, 256, 128, 256),
+                                              (1024, 12288, 512, 64, 256), (300, 12288, 256, 64, 192),
+                                              (300, 12200, 256, 32, 192), (2048, 12288, 256, 128, 256)])
+def test_the_tile_the_library_picks_for_wide_outputs(rt, m, n, k, group, tile):
+    """Shapes for which the library's own estimate picks the 256- and 192-wide tiles of the CTA-pair kernel, with
+    more tiles than clusters (each cluster walks several tiles: both accumulator buffers, rings that carry on
+    across tiles), ragged M and N, f32 and bf16 outputs, nothing written past y."""
+    packed, sb = synth.q4_bank(0x7E550500 + n + m, n, k, group)
+    packed, sb = packed.view(np.uint8).reshape(-1), sb.reshape(-1)
+    x = synth.normal_bf16(0x7E550507 + m, m * k)
+    pad = 4096
+    out = run_gemm(rt, x, packed, sb, m, n, k, group, pad=pad)
+    assert rt.last_prefill_tile() == (tile, 1), rt.last_prefill_tile()
+    assert np.all(out[m * n:] == SENTINEL_F32), "wrote past y"
+    got = out[: m * n].reshape(m, n)
+    assert np.all(np.isfinite(got)) and np.all(got != SENTINEL_F32)
+    want = api.q4_dense_gemm(packed, sb, x, m, n, k, group)
+    assert_north_star(got, want, f"prefill {m}x{n}x{k} g{group} tile {tile}")
+    _check_rows_against_the_oracle(got, packed, sb, x, _subset_rows(m), n, k, group, f"tile {tile} rows")
+    gb = run_gemm(rt, x, packed, sb, m, n, k, group, pad=pad, y_as_bf16=True)
+    assert np.array_equal(gb[: m * n], synth.f32_to_bf16_bits(got.reshape(-1)))
+    assert np.all(gb[m * n:] == 0xA5A5), "wrote past y (bf16)"
+
+
+def test_the_benchmarked_prefill_shape(rt):
+    """BASELINE config: X [2048, 4096] bf16 ~ N(0, 1) against a 12288 x 4096 bank of group 64 - the 256-wide tile of
+    the CTA-pair kernel, six tiles per cluster. Rows either side of every tile boundary against the oracle (the
+    full product is 1e11 multiply-adds on the host), every output through the row and column sums, and 64 rows
+    against the small-batch kernel, whose order of summation the reference's recorded vectors pin."""
+    m, n, k, group = 2048, 12288, 4096, 64
+    packed, sb = synth.q4_bank(0x7E550030, n, k, group)
+    packed, sb = packed.view(np.uint8).reshape(-1), sb.reshape(-1)
+    x = synth.normal_bf16(0x7E550031, m * k)
+    out = run_gemm(rt, x, packed, sb, m, n, k, group, pad=4096)
+    assert rt.last_prefill_tile() == (256, 1), rt.last_prefill_tile()
+    assert np.all(out[m * n:] == SENTINEL_F32), "wrote past y"
+    got = out[: m * n].reshape(m, n)
+    assert np.all(np.isfinite(got)) and np.all(got != SENTINEL_F32)
+    rows = _subset_rows(m)
+    _check_rows_against_the_oracle(got, packed, sb, x, rows, n, k, group, "2048x12288x4096 rows")
+    _check_sums_against_the_oracle(got, packed, sb, x, m, n, k, group, "2048x12288x4096")
+    bank, xb = upload_bank(rt, packed, sb), rt.buffer_from(x)
+    for r0 in range(0, m, 256):  # eight rows of every row tile
+        yc = seeded_f32(rt, 8 * n)
+        nn.gemm_q4_mlx(rt, bank, xb.view(r0 * k * 2, 8 * k * 2), yc, nn.QuantShape(n, k, group), 8)
+        simd = yc.read(np.float32, 8 * n).reshape(8, n)
+        yc.free()
+        assert_north_star(got[r0:r0 + 8], simd, f"rows {r0}.. against the small-batch kernel")
+        assert np.max(np.abs(got[r0:r0 + 8] - simd)) < 2e-3
+    for b in (bank.packed, bank.scales_biases, xb):
+        b.free()
+
+
+@pytest.mark.parametrize("pair", [1, 0])
+@pytest.mark.parametrize("tile", [128, 192, 256])
+def test_every_compiled_tile_on_ragged_shapes(rt, tile, pair):
+    """Each tile width of both kernels (CTA pair and single CTA), forced through the runtime's tuning hook, on
+    ragged shapes: fewer tiles than clusters, and several tiles per cluster."""
+    rt.set_prefill_tile(tile, pair)
+    try:
+        for m, n, k, group in ((300, 520, 384, 32), (129, 1000, 256, 64), (40, 72, 2048, 64), (700, 20011, 128, 128),
+                               (8, 4096, 1024, 64)):
+            packed, sb = synth.q4_bank(0x7E550600 + n, n, k, group)
+            packed, sb = packed.view(np.uint8).reshape(-1), sb.reshape(-1)
+            x = synth.normal_bf16(0x7E550607 + m, m * k)
+            out = run_gemm(rt, x, packed, sb, m, n, k, group, pad=1024)
+            assert rt.last_prefill_tile() == (tile, pair), rt.last_prefill_tile()
+            assert np.all(out[m * n:] == SENTINEL_F32), f"tile {tile} pair {pair}: wrote past y"
+            got = out[: m * n].reshape(m, n)
+            assert np.all(got != SENTINEL_F32), f"tile {tile} pair {pair}: unwritten output"
+            want = api.q4_dense_gemm(packed, sb, x, m, n, k, group)
+            assert_north_star(got, want, f"tile {tile} pair {pair} {m}x{n}x{k} g{group}")
+            rows = _subset_rows(m)[:12]
+            _check_rows_against_the_oracle(got, packed, sb, x, rows, n, k, group, f"tile {tile} pair {pair}")
+    finally:
+        rt.set_prefill_tile(0, -1)
+    with pytest.raises(nn.TesslError, match="tile_n 100"):
+        rt.set_prefill_tile(100, -1)
+
+
 def test_rows_of_any_magnitude_survive_the_f16_operands(rt):
     """The per-row power-of-two rescale: rows scaled by 2^-40 .. 2^+60 give the
     correspondingly scaled outputs, a zero row gives zeros."""
