@@ -175,12 +175,7 @@ Result launch_tma(TesslRuntime *rt, const Q4GemvParams &p)
     tp.stages = stages;
     tp.head_stages = (uint32_t)cfg.head_stages;
     const size_t smem = (size_t)warps * stages * (stage_bytes + 8);
-    static size_t smem_set = 0;
-    if (smem > smem_set) {
-        TESSL_TRY(cuda_check(rt, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
-                             "q4_gemv_tma: shared memory opt-in"));
-        smem_set = smem;
-    }
+    TESSL_TRY(smem_opt_in(rt, reinterpret_cast<const void *>(kernel), smem, "q4_gemv_tma: shared memory opt-in"));
     const uint32_t grid = std::min<uint32_t>(rb, (uint32_t)(rt->sm_count * cfg.blocks_per_sm));
     cudaLaunchConfig_t lc{};
     lc.gridDim = dim3(grid), lc.blockDim = dim3(cfg.consumers * 32), lc.dynamicSmemBytes = smem;
@@ -250,34 +245,11 @@ Result launch_mma_one(TesslRuntime *rt, const Q4GemvParams &p, int m, const MmaW
     const uint32_t gpr = p.cols >> p.group_shift;
     const uint32_t part = BATCH ? q4m::kConsumers * 16 * 8 * 4 : q4m::kConsumers * 16 * 4;
     const uint32_t stage_bytes = 16 * ((p.cols >> 1) + q4m::kRowPad) + 16 * gpr * 4 + part;
-    uint32_t stages = std::min<uint32_t>(8u, (216u * 1024u) / (stage_bytes + 24));
-    // TESSL_B200_GEMV_MMA_STAGES caps the ring depth (tuning runs).
-    static int cap = -1;
-    if (cap < 0) {
-        const char *e = std::getenv("TESSL_B200_GEMV_MMA_STAGES");
-        cap = e ? std::max(1, std::atoi(e)) : 0;
-    }
-    if (cap > 0) stages = std::min<uint32_t>(stages, (uint32_t)cap);
+    const uint32_t x_stage = 16 + q4m::kConsumers * q4m::kXStageBytes;  // the warps' staged slices of x (M = 1)
+    uint32_t stages = std::min<uint32_t>(8u, (216u * 1024u - x_stage) / (stage_bytes + 24));
     mp.stages = stages;
-    const size_t smem = (size_t)stages * (stage_bytes + 24);
-    static size_t smem_set = 0;
-    if (smem > smem_set) {
-        TESSL_TRY(cuda_check(rt, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
-                             "q4_gemv_mma: shared memory opt-in"));
-        // All of the SM's configurable memory as shared memory, so that a short ring leaves room
-        // for the next launch's block beside this one's.
-        TESSL_TRY(cuda_check(rt, cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
-                                                      (int)cudaSharedmemCarveoutMaxShared),
-                             "q4_gemv_mma: shared memory carve-out"));
-        smem_set = smem;
-        if (std::getenv("TESSL_B200_DEBUG_OCCUPANCY")) {
-            int nb = 0;
-            cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nb, kernel, q4m::kThreads, smem);
-            cudaFuncAttributes fa{};
-            cudaFuncGetAttributes(&fa, kernel);
-            std::fprintf(stderr, "q4_gemv_mma: %d regs, %zu B dynamic smem, %d blocks/SM\n", fa.numRegs, smem, nb);
-        }
-    }
+    const size_t smem = (size_t)stages * (stage_bytes + 24) + x_stage;
+    TESSL_TRY(smem_opt_in(rt, reinterpret_cast<const void *>(kernel), smem, "q4_gemv_mma: shared memory opt-in", true));
     const uint32_t grid = std::min<uint32_t>(rb, (uint32_t)rt->sm_count);
     cudaLaunchConfig_t lc{};
     lc.gridDim = dim3(grid), lc.blockDim = dim3(q4m::kThreads), lc.dynamicSmemBytes = smem;

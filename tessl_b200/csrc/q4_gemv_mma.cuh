@@ -59,6 +59,7 @@ using q4k::smem_u32;
 constexpr int kConsumers = 16;
 constexpr int kThreads = (kConsumers + 2) * 32;
 constexpr uint32_t kRowPad = 32;  // bytes; row pitch = K / 2 + 32
+constexpr uint32_t kXStageBytes = 512 + 32;  // a warp's staged slice of x: B fragments and up to 8 group sums
 
 struct Seg {
     const uint8_t *packed0;
@@ -135,6 +136,9 @@ __global__ void __launch_bounds__(kThreads, TESSL_GEMV_MMA_MIN_BLOCKS) q4_gemv_m
     auto full = [&](uint32_t s) { return bars + 8 * s; };
     auto empty = [&](uint32_t s) { return bars + 8 * (S + s); };
     auto done = [&](uint32_t s) { return bars + 8 * (2 * S + s); };
+    // M = 1: each warp stages its slice of x once (512 bytes of B fragments + the group sums) and the
+    // lanes read their fragments back, instead of every lane converting the 64 values it holds.
+    const uint32_t xstage = ((bars + 24 * S + 15u) & ~15u) + (uint32_t)warp * kXStageBytes;
 
     const uint32_t rb_lo = (uint32_t)((uint64_t)p.total_rb * blockIdx.x / gridDim.x);
     const uint32_t rb_hi = (uint32_t)((uint64_t)p.total_rb * (blockIdx.x + 1) / gridDim.x);
@@ -312,9 +316,76 @@ __global__ void __launch_bounds__(kThreads, TESSL_GEMV_MMA_MIN_BLOCKS) q4_gemv_m
         // nibble-pair extraction below produces.
         uint32_t xb[SW][4];
         float xs[NGS];  // group sums of the activations: column g (BATCH) or the vector (M = 1)
+        // Q4: the nibbles go to the MMA as the bf16 bit patterns 0..15 and 16 x (0..15), i.e. q * 2^-133 (the
+        // subnormal range and the first binade of bf16 are one linear scale), so the activations carry the
+        // rest: times 2^e (e puts the slice's largest magnitude of this row of x near 2^100, so that every
+        // product is a normal f32), the partners of the odd nibbles divided by 16 as well. Both are changes
+        // of the exponent field only, hence exact; `cw` = 2^(133 - e) undoes them in the fold.
+        float cw = 0.0f;
         {
             const uint32_t n = BATCH ? min(g, p.m - 1) : 0u;
             const uint16_t *xrow = p.x + (size_t)n * p.x_pitch;
+            int e = 0;
+            if constexpr (BATCH && !Q8) {
+                uint32_t amax = 0;
+#pragma unroll
+                for (int jj = 0; jj < NGS; ++jj) {
+#pragma unroll
+                    for (int u = 0; u < WPG; ++u) {
+                        const uint4 r = __ldg(reinterpret_cast<const uint4 *>(xrow + k0 + jj * G + t * (G / 4) + 8 * u));
+                        amax = max(amax, max(max(r.x & 0x7fffu, (r.x >> 16) & 0x7fffu), max(r.y & 0x7fffu, (r.y >> 16) & 0x7fffu)));
+                        amax = max(amax, max(max(r.z & 0x7fffu, (r.z >> 16) & 0x7fffu), max(r.w & 0x7fffu, (r.w >> 16) & 0x7fffu)));
+                    }
+                }
+                amax = max(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+                amax = max(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+                if ((amax >> 7) != 0) {
+                    const int maxexp = (int)(amax >> 7) - 127;
+                    e = min(126, max(100, maxexp + 6)) - maxexp;
+                    cw = __uint_as_float((uint32_t)(127 + 133 - e) << 23);
+                }
+            }
+            // bf16 bits times 2^ee; zeros, subnormals and whatever would leave the normal range become 0
+            auto scaled = [](uint32_t b, int ee) -> uint32_t {
+                const int ex = (int)((b >> 7) & 0xffu), nx = ex + ee;
+                return (ex == 0 || nx < 1 || nx > 254) ? 0u : ((b & 0x807fu) | ((uint32_t)nx << 7));
+            };
+            auto pair = [&](uint32_t lo, uint32_t hi, int ee) { return scaled(lo & 0xffffu, ee) | (scaled(hi & 0xffffu, ee) << 16); };
+            if constexpr (!BATCH && !Q8) {
+                constexpr uint32_t NW = 4 * SW;  // 8-column words of the slice: lane L < NW handles word L
+                uint4 r = make_uint4(0u, 0u, 0u, 0u);
+                if ((uint32_t)lane < NW) r = __ldg(reinterpret_cast<const uint4 *>(xrow + k0 + 8 * lane));
+                uint32_t amax = max(max(r.x & 0x7fffu, (r.x >> 16) & 0x7fffu), max(r.y & 0x7fffu, (r.y >> 16) & 0x7fffu));
+                amax = max(amax, max(max(r.z & 0x7fffu, (r.z >> 16) & 0x7fffu), max(r.w & 0x7fffu, (r.w >> 16) & 0x7fffu)));
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) amax = max(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+                if ((amax >> 7) != 0) {
+                    const int maxexp = (int)(amax >> 7) - 127;
+                    e = min(126, max(100, maxexp + 6)) - maxexp;
+                    cw = __uint_as_float((uint32_t)(127 + 133 - e) << 23);
+                }
+                if ((uint32_t)lane < NW) {
+                    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(xstage + lane * 16), "r"(pair(r.x, r.z, e)),
+                                 "r"(pair(r.x >> 16, r.z >> 16, e - 4)), "r"(pair(r.y, r.w, e)), "r"(pair(r.y >> 16, r.w >> 16, e - 4))
+                                 : "memory");
+                }
+                float part = (dev::bf16_lo(r.x) + dev::bf16_hi(r.x)) + (dev::bf16_lo(r.y) + dev::bf16_hi(r.y));
+                part += (dev::bf16_lo(r.z) + dev::bf16_hi(r.z)) + (dev::bf16_lo(r.w) + dev::bf16_hi(r.w));
+#pragma unroll
+                for (int o = 1; o < 4 * WPG && o < 32; o <<= 1) part += __shfl_xor_sync(0xffffffffu, part, o);  // a group: 4 WPG lanes
+                const float gsum = __shfl_sync(0xffffffffu, part, (lane * 4 * WPG) & 31);
+                if (lane < NGS) asm volatile("st.shared.f32 [%0], %1;" ::"r"(xstage + 512 + lane * 4), "f"(gsum) : "memory");
+                __syncwarp();
+#pragma unroll
+                for (int jj = 0; jj < NGS; ++jj) {
+#pragma unroll
+                    for (int u = 0; u < WPG; ++u) {
+                        const uint4 f = q4k::lds128(xstage + (jj * 4 * WPG + t * WPG + u) * 16);
+                        xb[jj * WPG + u][0] = f.x, xb[jj * WPG + u][1] = f.y, xb[jj * WPG + u][2] = f.z, xb[jj * WPG + u][3] = f.w;
+                    }
+                    xs[jj] = __uint_as_float(lds32(xstage + 512 + jj * 4));
+                }
+            } else
 #pragma unroll
             for (int jj = 0; jj < NGS; ++jj) {
                 float part = 0.0f;
@@ -336,10 +407,10 @@ __global__ void __launch_bounds__(kThreads, TESSL_GEMV_MMA_MIN_BLOCKS) q4_gemv_m
                         part += (x0 + x1) + (x2 + x3);
                     } else {
                         const uint4 r = __ldg(reinterpret_cast<const uint4 *>(xrow + k));
-                        xb[jj * WPG + u][0] = __byte_perm(r.x, r.z, 0x5410);  // x0, x4
-                        xb[jj * WPG + u][1] = __byte_perm(r.x, r.z, 0x7632);  // x1, x5
-                        xb[jj * WPG + u][2] = __byte_perm(r.y, r.w, 0x5410);  // x2, x6
-                        xb[jj * WPG + u][3] = __byte_perm(r.y, r.w, 0x7632);  // x3, x7
+                        xb[jj * WPG + u][0] = pair(r.x, r.z, e);                  // x0, x4
+                        xb[jj * WPG + u][1] = pair(r.x >> 16, r.z >> 16, e - 4);  // (x1, x5) / 16
+                        xb[jj * WPG + u][2] = pair(r.y, r.w, e);                  // x2, x6
+                        xb[jj * WPG + u][3] = pair(r.y >> 16, r.w >> 16, e - 4);  // (x3, x7) / 16
                         part += (dev::bf16_lo(r.x) + dev::bf16_hi(r.x)) + (dev::bf16_lo(r.y) + dev::bf16_hi(r.y));
                         part += (dev::bf16_lo(r.z) + dev::bf16_hi(r.z)) + (dev::bf16_lo(r.w) + dev::bf16_hi(r.w));
                     }
@@ -351,7 +422,10 @@ __global__ void __launch_bounds__(kThreads, TESSL_GEMV_MMA_MIN_BLOCKS) q4_gemv_m
         }
         // BATCH: this lane's outputs are batch columns 2 t and 2 t + 1; their group sums live in quads 2 t and 2 t + 1.
         float xs0[BATCH ? NGS : 1], xs1[BATCH ? NGS : 1];
+        float cw0 = cw, cw1 = cw;  // the multipliers of this lane's two output columns
         if constexpr (BATCH) {
+            cw0 = __shfl_sync(0xffffffffu, cw, (2 * t) * 4);
+            cw1 = __shfl_sync(0xffffffffu, cw, (2 * t + 1) * 4);
 #pragma unroll
             for (int jj = 0; jj < NGS; ++jj) {
                 xs0[jj] = __shfl_sync(0xffffffffu, xs[jj], (2 * t) * 4);
@@ -401,19 +475,30 @@ __global__ void __launch_bounds__(kThreads, TESSL_GEMV_MMA_MIN_BLOCKS) q4_gemv_m
 #pragma unroll
                 for (int jj = 0; jj < NGS; ++jj) {
                     const uint32_t a = wl[jj * WPG + u], b = wh[jj * WPG + u];
-                    // nibble pairs (i, i + 4) as two bf16 values 128 + q: exactly an A-fragment register
-                    // (the shifts share the LOP3s' pipe, this kernel's busiest; `mul.hi` by 2^28 on the
-                    // multiply pipe instead measured 40% slower)
-                    const uint32_t a0 = and_or(a, 0x000f000fu, kMagic), b0 = and_or(b, 0x000f000fu, kMagic);
-                    const uint32_t a1 = and_or(a >> 4, 0x000f000fu, kMagic), b1 = and_or(b >> 4, 0x000f000fu, kMagic);
-                    mma_bf16(d[jj], a0, b0, a1, b1, xb[jj * WPG + u][0], xb[jj * WPG + u][1]);  // columns 0,4 | 1,5
+                    if constexpr (Q8) {
+                        // nibble pairs (i, i + 4) as two bf16 values 128 + q: exactly an A-fragment register
+                        const uint32_t a0 = and_or(a, 0x000f000fu, kMagic), b0 = and_or(b, 0x000f000fu, kMagic);
+                        const uint32_t a1 = and_or(a >> 4, 0x000f000fu, kMagic), b1 = and_or(b >> 4, 0x000f000fu, kMagic);
+                        mma_bf16(d[jj], a0, b0, a1, b1, xb[jj * WPG + u][0], xb[jj * WPG + u][1]);  // columns 0,4 | 1,5
+                    } else {
+                        // nibble pairs (0, 4) and 16 x (1, 5) in place: five ALU instructions per word instead of
+                        // seven (these share the busiest pipe of the kernel), and nothing to subtract afterwards
+                        mma_bf16(d[jj], a & 0x000f000fu, b & 0x000f000fu, a & 0x00f000f0u, b & 0x00f000f0u, xb[jj * WPG + u][0],
+                                 xb[jj * WPG + u][1]);
+                    }
                 }
 #pragma unroll
                 for (int jj = 0; jj < NGS; ++jj) {
                     const uint32_t a = wl[jj * WPG + u], b = wh[jj * WPG + u];
-                    const uint32_t a2 = and_or(a >> 8, 0x000f000fu, kMagic), b2 = and_or(b >> 8, 0x000f000fu, kMagic);
-                    const uint32_t a3 = and_or(a >> 12, 0x000f000fu, kMagic), b3 = and_or(b >> 12, 0x000f000fu, kMagic);
-                    mma_bf16(d[jj], a2, b2, a3, b3, xb[jj * WPG + u][2], xb[jj * WPG + u][3]);  // columns 2,6 | 3,7
+                    if constexpr (Q8) {
+                        const uint32_t a2 = and_or(a >> 8, 0x000f000fu, kMagic), b2 = and_or(b >> 8, 0x000f000fu, kMagic);
+                        const uint32_t a3 = and_or(a >> 12, 0x000f000fu, kMagic), b3 = and_or(b >> 12, 0x000f000fu, kMagic);
+                        mma_bf16(d[jj], a2, b2, a3, b3, xb[jj * WPG + u][2], xb[jj * WPG + u][3]);  // columns 2,6 | 3,7
+                    } else {
+                        const uint32_t as = a >> 8, bs = b >> 8;
+                        mma_bf16(d[jj], as & 0x000f000fu, bs & 0x000f000fu, as & 0x00f000f0u, bs & 0x00f000f0u, xb[jj * WPG + u][2],
+                                 xb[jj * WPG + u][3]);
+                    }
                 }
             }
 #pragma unroll
@@ -422,10 +507,17 @@ __global__ void __launch_bounds__(kThreads, TESSL_GEMV_MMA_MIN_BLOCKS) q4_gemv_m
                     const uint32_t pl = lds32(sb_lo + jj * 4), ph2 = lds32(sb_hi + jj * 4);
                     const float sl = dev::bf16_lo(pl), bl = dev::bf16_hi(pl), sh = dev::bf16_lo(ph2), bh = dev::bf16_hi(ph2);
                     const int cls = jj & 3;  // a constant once the loop is unrolled
-                    acc[0][cls] = fmaf(sl, fmaf(kOffset, xs0[jj], d[jj][0]), fmaf(bl, xs0[jj], acc[0][cls]));
-                    acc[1][cls] = fmaf(sl, fmaf(kOffset, xs1[jj], d[jj][1]), fmaf(bl, xs1[jj], acc[1][cls]));
-                    acc[2][cls] = fmaf(sh, fmaf(kOffset, xs0[jj], d[jj][2]), fmaf(bh, xs0[jj], acc[2][cls]));
-                    acc[3][cls] = fmaf(sh, fmaf(kOffset, xs1[jj], d[jj][3]), fmaf(bh, xs1[jj], acc[3][cls]));
+                    if constexpr (Q8) {
+                        acc[0][cls] = fmaf(sl, fmaf(kOffset, xs0[jj], d[jj][0]), fmaf(bl, xs0[jj], acc[0][cls]));
+                        acc[1][cls] = fmaf(sl, fmaf(kOffset, xs1[jj], d[jj][1]), fmaf(bl, xs1[jj], acc[1][cls]));
+                        acc[2][cls] = fmaf(sh, fmaf(kOffset, xs0[jj], d[jj][2]), fmaf(bh, xs0[jj], acc[2][cls]));
+                        acc[3][cls] = fmaf(sh, fmaf(kOffset, xs1[jj], d[jj][3]), fmaf(bh, xs1[jj], acc[3][cls]));
+                    } else {
+                        acc[0][cls] = fmaf(sl, d[jj][0] * cw0, fmaf(bl, xs0[jj], acc[0][cls]));
+                        acc[1][cls] = fmaf(sl, d[jj][1] * cw1, fmaf(bl, xs1[jj], acc[1][cls]));
+                        acc[2][cls] = fmaf(sh, d[jj][2] * cw0, fmaf(bh, xs0[jj], acc[2][cls]));
+                        acc[3][cls] = fmaf(sh, d[jj][3] * cw1, fmaf(bh, xs1[jj], acc[3][cls]));
+                    }
                 } else {
                     dlo[jj] = d[jj][0], dhi[jj] = d[jj][2];  // every column holds the same vector: d[1] == d[0]
                 }
@@ -453,8 +545,8 @@ __global__ void __launch_bounds__(kThreads, TESSL_GEMV_MMA_MIN_BLOCKS) q4_gemv_m
                     const uint32_t jj = 4 * q + t;
                     if (jj < (uint32_t)NGS) {
                         const uint32_t pl = lds32(sb_lo + jj * 4), ph2 = lds32(sb_hi + jj * 4);
-                        vlo = fmaf(dev::bf16_lo(pl), fmaf(kOffset, xg, dl), fmaf(dev::bf16_hi(pl), xg, vlo));
-                        vhi = fmaf(dev::bf16_lo(ph2), fmaf(kOffset, xg, dh), fmaf(dev::bf16_hi(ph2), xg, vhi));
+                        vlo = fmaf(dev::bf16_lo(pl), dl * cw, fmaf(dev::bf16_hi(pl), xg, vlo));
+                        vhi = fmaf(dev::bf16_lo(ph2), dh * cw, fmaf(dev::bf16_hi(ph2), xg, vhi));
                     }
                 }
                 vlo += __shfl_xor_sync(0xffffffffu, vlo, 1), vhi += __shfl_xor_sync(0xffffffffu, vhi, 1);
