@@ -298,6 +298,38 @@ TESSL_API int32_t tessl_gemv_q8(TesslRuntime *rt, TesslBuf packed, TesslBuf scal
 TESSL_API int32_t tessl_gemm_q8_mlx(TesslRuntime *rt, TesslBuf codes, TesslBuf scales_biases, TesslBuf x_bf16, TesslBuf y,
                           TesslQuantShape shape, uint32_t m, uint32_t y_as_bf16, char *err, size_t err_len);
 
+/* ------------------------------------------------------ embedding gather --- */
+
+/* `nn::embed_lookup_q4_mlx` (src/nn.rs:3592-3658; kernels/embed_lookup.metal:7-38):
+ * out[m, :] = the dequantized row token_ids[m] of an MLX Q4 table [vocab, hidden]
+ * (w = scale * q + bias, separate multiply and add), f32 [n_tokens, hidden];
+ * token_ids u32 [n_tokens]; an id >= vocab gives a row of zeros. First operator
+ * of every decode step (src/qwen35_model.rs:1476). */
+TESSL_API int32_t tessl_embed_lookup_q4_mlx(TesslRuntime *rt, TesslQ4MlxBank bank, TesslBuf token_ids, TesslBuf out,
+                                  uint32_t vocab, uint32_t hidden, uint32_t group_size, uint32_t n_tokens, char *err,
+                                  size_t err_len);
+
+/* ------------------------------------------ either side of a projection --- */
+
+/* `qwen35::rms_norm` (src/qwen35.rs:2654-2695; kernels/qwen35_mlp.metal:76-122):
+ * out[r, :] = x[r, :] * rsqrt(mean(x[r, :]^2) + eps) * (1 + w[:]); x f32 [rows, dim],
+ * w f32 [dim] as the checkpoint holds it, out f32 or (out_as_bf16 != 0) bf16 -
+ * the activations a Q4 projection reads. An f32 out may be x itself. */
+TESSL_API int32_t tessl_qwen35_rms_norm(TesslRuntime *rt, TesslBuf x, TesslBuf w, TesslBuf out, uint32_t out_as_bf16,
+                              uint32_t rows, uint32_t dim, float eps, char *err, size_t err_len);
+
+/* `qwen35::residual_add` for dense operands (src/qwen35.rs:2586-2623): resid += y,
+ * f32 [rows, width]. */
+TESSL_API int32_t tessl_qwen35_residual_add(TesslRuntime *rt, TesslBuf y, TesslBuf resid, uint32_t rows, uint32_t width,
+                                  char *err, size_t err_len);
+
+/* `qwen35::add_rms_norm` (src/qwen35.rs:2697-2747; kernels/qwen35_mlp.metal:124-171):
+ * resid += y, then out = rms_norm(resid) * (1 + w), in one launch; bit-identical
+ * to tessl_qwen35_residual_add followed by tessl_qwen35_rms_norm. */
+TESSL_API int32_t tessl_qwen35_add_rms_norm(TesslRuntime *rt, TesslBuf y, TesslBuf resid, TesslBuf w, TesslBuf out,
+                                  uint32_t out_as_bf16, uint32_t rows, uint32_t dim, float eps, char *err,
+                                  size_t err_len);
+
 /* ------------------------------------------------------- parity helpers --- */
 
 /* Debug kernels for the bit-exact parity gates: the bank's nibbles as one

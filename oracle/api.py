@@ -239,3 +239,29 @@ def silu_f32(x) -> np.float32:
 def fnv1a_words(words: np.ndarray) -> int:
     w = np.ascontiguousarray(words, np.uint32).reshape(-1)
     return lib().orc_fnv1a_words(w, w.size)
+
+
+def embed_lookup_q4_mlx(packed, sb, token_ids, vocab, hidden, group) -> np.ndarray:
+    """kernels/embed_lookup.metal:7-38 of the reference project: out[m, :] = the dequantized row
+    token_ids[m] (scale * q + bias in f32; the product is exact, so a fused multiply-add gives the
+    same bits), a row of zeros for an id outside the table. f32 [n_tokens, hidden]."""
+    ids = np.ascontiguousarray(token_ids, np.uint32).reshape(-1)
+    out = np.zeros((ids.size, hidden), np.float32)
+    p = _c(packed, np.uint8).reshape(vocab, hidden // 2)
+    s = _c(sb, np.uint16).reshape(vocab, (hidden // group) * 2)
+    for m, tid in enumerate(ids):
+        if tid < vocab:
+            out[m] = q4_dequant(p[tid], s[tid], 1, hidden, group)[0]
+    return out
+
+
+def qwen35_rms_norm_f64(x, w, rows, dim, eps, resid_add=None) -> np.ndarray:
+    """kernels/qwen35_mlp.metal:76-171 of the reference project in f64: out = v * rsqrt(mean(v^2) + eps)
+    * (1 + w) with v = x (+ y for the fused add), `1 + w` formed in f32 as the kernel forms it."""
+    v = np.asarray(x, np.float32).reshape(rows, dim)
+    if resid_add is not None:
+        v = v + np.asarray(resid_add, np.float32).reshape(rows, dim)  # the f32 add of the kernel
+    v64 = v.astype(np.float64)
+    inv = 1.0 / np.sqrt((v64 * v64).mean(axis=1, keepdims=True) + np.float64(np.float32(eps)))
+    wp = (np.float32(1.0) + np.asarray(w, np.float32).reshape(dim)).astype(np.float64)
+    return v64 * inv * wp

@@ -93,6 +93,10 @@ SIGNATURES = {
     "tessl_q4_weight_gate_up_silu": (C.c_int32, [_RT, Q4MlxBank, Q4MlxBank, _u32, _u32, Buf, Buf, _u32] + _ERR),
     "tessl_gemv_q8": (C.c_int32, [_RT, Buf, Buf, Buf, Buf, Buf, _u32, _u32, _u32] + _ERR),
     "tessl_gemm_q8_mlx": (C.c_int32, [_RT, Buf, Buf, Buf, Buf, QuantShape, _u32, _u32] + _ERR),
+    "tessl_embed_lookup_q4_mlx": (C.c_int32, [_RT, Q4MlxBank, Buf, Buf, _u32, _u32, _u32, _u32] + _ERR),
+    "tessl_qwen35_rms_norm": (C.c_int32, [_RT, Buf, Buf, Buf, _u32, _u32, _u32, C.c_float] + _ERR),
+    "tessl_qwen35_residual_add": (C.c_int32, [_RT, Buf, Buf, _u32, _u32] + _ERR),
+    "tessl_qwen35_add_rms_norm": (C.c_int32, [_RT, Buf, Buf, Buf, Buf, _u32, _u32, _u32, C.c_float] + _ERR),
     "tessl_q4_mlx_unpack": (C.c_int32, [_RT, Q4MlxBank, QuantShape, Buf] + _ERR),
     "tessl_q4_mlx_dequant": (C.c_int32, [_RT, Q4MlxBank, QuantShape, Buf] + _ERR),
 }

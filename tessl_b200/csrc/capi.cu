@@ -492,6 +492,35 @@ int32_t tessl_gemm_q8_mlx(TesslRuntime *rt, TesslBuf codes, TesslBuf scales_bias
     });
 }
 
+int32_t tessl_embed_lookup_q4_mlx(TesslRuntime *rt, TesslQ4MlxBank bank, TesslBuf token_ids, TesslBuf out, uint32_t vocab,
+                                  uint32_t hidden, uint32_t group_size, uint32_t n_tokens, char *err, size_t err_len)
+{
+    return guarded(rt, err, err_len, true, [&] {
+        return tessl::nn::embed_lookup_q4_mlx(rt, bank, token_ids, out, vocab, hidden, group_size, n_tokens);
+    });
+}
+
+int32_t tessl_qwen35_rms_norm(TesslRuntime *rt, TesslBuf x, TesslBuf w, TesslBuf out, uint32_t out_as_bf16, uint32_t rows,
+                              uint32_t dim, float eps, char *err, size_t err_len)
+{
+    return guarded(rt, err, err_len, true,
+                   [&] { return tessl::nn::qwen35_rms_norm(rt, x, w, out, out_as_bf16 != 0, rows, dim, eps); });
+}
+
+int32_t tessl_qwen35_residual_add(TesslRuntime *rt, TesslBuf y, TesslBuf resid, uint32_t rows, uint32_t width, char *err,
+                                  size_t err_len)
+{
+    return guarded(rt, err, err_len, true, [&] { return tessl::nn::qwen35_residual_add(rt, y, resid, rows, width); });
+}
+
+int32_t tessl_qwen35_add_rms_norm(TesslRuntime *rt, TesslBuf y, TesslBuf resid, TesslBuf w, TesslBuf out,
+                                  uint32_t out_as_bf16, uint32_t rows, uint32_t dim, float eps, char *err, size_t err_len)
+{
+    return guarded(rt, err, err_len, true, [&] {
+        return tessl::nn::qwen35_add_rms_norm(rt, y, resid, w, out, out_as_bf16 != 0, rows, dim, eps);
+    });
+}
+
 int32_t tessl_q4_mlx_unpack(TesslRuntime *rt, TesslQ4MlxBank bank, TesslQuantShape shape, TesslBuf out_u8, char *err,
                             size_t err_len)
 {

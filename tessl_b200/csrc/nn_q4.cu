@@ -61,6 +61,38 @@ __global__ void q4_dequant_kernel(const uint8_t *packed, const uint32_t *sb, flo
     out[e + 1] = __fadd_rn(__fmul_rn(scale, (float)(b >> 4)), bias);
 }
 
+/// One thread per 32 consecutive columns of one token's row (16 packed bytes, never more than one
+/// quantization group): a 128-bit load of the nibbles, one scale/bias pair, eight 128-bit stores.
+/// A token id outside the table gives a row of zeros (kernels/embed_lookup.metal:24-27 of the
+/// reference project).
+__global__ void embed_lookup_q4_mlx_kernel(const uint8_t *packed, const uint32_t *sb, const uint32_t *token_ids, float *out,
+                                           uint32_t hidden, uint32_t group_shift, uint32_t vocab, uint64_t total32)
+{
+    const uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total32) return;
+    const uint32_t per_row = hidden / 32;
+    const uint32_t m = (uint32_t)(i / per_row), c = (uint32_t)(i % per_row);
+    const uint32_t tid = token_ids[m];
+    float4 *o = reinterpret_cast<float4 *>(out + (size_t)m * hidden + (size_t)c * 32);
+    if (tid >= vocab) {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) o[k] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        return;
+    }
+    const uint4 w = dev::ldg_stream16(packed + (size_t)tid * (hidden / 2) + (size_t)c * 16);
+    const uint32_t pair = sb[(size_t)tid * (hidden >> group_shift) + ((c * 32) >> group_shift)];
+    const float scale = dev::bf16_lo(pair), bias = dev::bf16_hi(pair);
+    const uint32_t words[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        float v[8];
+#pragma unroll
+        for (int n = 0; n < 8; ++n) v[n] = __fadd_rn(__fmul_rn(scale, (float)((words[k] >> (4 * n)) & 15u)), bias);
+        o[2 * k] = make_float4(v[0], v[1], v[2], v[3]);
+        o[2 * k + 1] = make_float4(v[4], v[5], v[6], v[7]);
+    }
+}
+
 uint32_t log2_u32(uint32_t v)
 {
     uint32_t s = 0;
@@ -694,6 +726,31 @@ Result gemm_q4_mlx(TesslRuntime *rt, const TesslQ4MlxBank &bank, const TesslBuf 
     p.epi = resid ? EPI_ADD_RESID : EPI_STORE;
     p.out_bf16 = out == OUT_BF16;
     return launch_q4_gemv(rt, p, (int)m, 1);
+}
+
+Result embed_lookup_q4_mlx(TesslRuntime *rt, const TesslQ4MlxBank &bank, const TesslBuf &token_ids, const TesslBuf &out,
+                           uint32_t vocab, uint32_t hidden, uint32_t group_size, uint32_t n_tokens)
+{
+    const char *what = "embed_lookup_q4_mlx";
+    const TesslQuantShape shape{vocab, hidden, group_size};
+    TESSL_TRY(q4_bank_validate(bank, shape, what));
+    const uint64_t total = elems(n_tokens, hidden);
+    TESSL_TRY(require(token_ids, n_tokens, 4, std::string(what) + " token_ids"));
+    TESSL_TRY(require(out, total, 4, std::string(what) + " out"));
+    const Named writes[] = {{"out", &out}};
+    const Named reads[] = {{"packed", &bank.packed}, {"scales_biases", &bank.scales_biases}, {"token_ids", &token_ids}};
+    TESSL_TRY(require_disjoint_writes(what, writes, 1, reads, 3));
+    if (total == 0) return ok();
+    TESSL_TRY(check_alignment(bank, what));
+    TESSL_TRY(require_aligned16(out, std::string(what) + " out"));
+    if (((uintptr_t)token_ids.ptr & 3u) != 0) return fmt("%s token_ids: device pointer must be 4-byte aligned", what);
+    const uint64_t total32 = total / 32;  // hidden is a multiple of the group size, itself a multiple of 32
+    embed_lookup_q4_mlx_kernel<<<(unsigned)((total32 + 127) / 128), 128, 0, rt->stream>>>(
+        static_cast<const uint8_t *>(bank.packed.ptr), static_cast<const uint32_t *>(bank.scales_biases.ptr),
+        static_cast<const uint32_t *>(token_ids.ptr), static_cast<float *>(out.ptr), hidden, log2_u32(group_size), vocab,
+        total32);
+    rt->dispatch_count += 1;
+    return cuda_check(rt, cudaGetLastError(), "embed_lookup_q4_mlx launch");
 }
 
 Result q4_mlx_unpack(TesslRuntime *rt, const TesslQ4MlxBank &bank, const TesslQuantShape &shape, const TesslBuf &out)

@@ -16,8 +16,8 @@
 // source rank, [16] this rank's own call counter, [17] a ticket counter of the
 // call's thread blocks), so the same launch can be replayed from a CUDA graph.
 // Larger slices are copied by several thread blocks; the last one to finish its
-// part (by ticket) does the completion handshake. Every wait is bounded (~2 s); on expiry the
-// runtime's status word is set and the kernel returns. There is no counterpart
+// part (by ticket) does the completion handshake. Every wait is bounded (~0.5 s unless the runtime's
+// peer-wait limit says otherwise); on expiry the runtime's status word is set and the kernel returns. There is no counterpart
 // in the reference (a single-device library).
 #include <algorithm>
 
@@ -31,6 +31,7 @@ struct PeerGatherParams {
     uint32_t *flags[8];  // flag words of every rank
     uint32_t rank, world;
     uint64_t bytes_per_rank;  // multiple of 16
+    long long wait_clocks;    // bound of every wait for a peer
     uint32_t *status;
 };
 
@@ -57,7 +58,7 @@ __device__ __forceinline__ bool wait_peers(const PeerGatherParams &p, uint32_t b
         const uint32_t *f = p.flags[p.rank] + base + threadIdx.x;
         const long long t0 = clock64();
         while ((int32_t)(ld_acquire_sys(f) - seq) < 0) {
-            if (clock64() - t0 > kWaitClocks) {
+            if (clock64() - t0 > p.wait_clocks) {
                 *(volatile uint32_t *)p.status = (0x50u << 24) | (code << 16) | threadIdx.x;
                 ok_ = false;
                 break;
@@ -124,6 +125,7 @@ Result peer_gather(TesslRuntime *rt, const TesslPeerGather &g)
     PeerGatherParams p{};
     for (uint32_t r = 0; r < g.world; ++r) p.buf[r] = static_cast<uint8_t *>(g.buffers[r]), p.flags[r] = g.flags[r];
     p.rank = g.rank, p.world = g.world, p.bytes_per_rank = g.bytes_per_rank;
+    p.wait_clocks = rt->peer_wait_clocks ? (long long)rt->peer_wait_clocks : kWaitClocks;
     p.status = rt->status_dev;
     cudaLaunchConfig_t lc{};
     // one block per 32 KiB of slice, at most 16: a few KB go fastest from one block, the LM head's

@@ -257,6 +257,13 @@ Result gemv_q8(TesslRuntime *rt, const TesslBuf &packed, const TesslBuf &scales,
                const TesslBuf &x, const TesslBuf &y, uint32_t rows, uint32_t cols, uint32_t group_size);
 Result gemm_q8_mlx(TesslRuntime *rt, const TesslBuf &codes, const TesslBuf &sb, const TesslBuf &x_bf16,
                    const TesslBuf &y, const TesslQuantShape &shape, uint32_t m, OutKind out);
+Result qwen35_rms_norm(TesslRuntime *rt, const TesslBuf &x, const TesslBuf &w, const TesslBuf &out, bool out_as_bf16,
+                       uint32_t rows, uint32_t dim, float eps);
+Result qwen35_residual_add(TesslRuntime *rt, const TesslBuf &y, const TesslBuf &resid, uint32_t rows, uint32_t width);
+Result qwen35_add_rms_norm(TesslRuntime *rt, const TesslBuf &y, const TesslBuf &resid, const TesslBuf &w, const TesslBuf &out,
+                           bool out_as_bf16, uint32_t rows, uint32_t dim, float eps);
+Result embed_lookup_q4_mlx(TesslRuntime *rt, const TesslQ4MlxBank &bank, const TesslBuf &token_ids, const TesslBuf &out,
+                           uint32_t vocab, uint32_t hidden, uint32_t group_size, uint32_t n_tokens);
 Result q4_mlx_unpack(TesslRuntime *rt, const TesslQ4MlxBank &bank, const TesslQuantShape &shape, const TesslBuf &out);
 Result q4_mlx_dequant(TesslRuntime *rt, const TesslQ4MlxBank &bank, const TesslQuantShape &shape,
                       const TesslBuf &out);

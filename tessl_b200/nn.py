@@ -291,6 +291,30 @@ def gemm_q8_mlx(rt: Runtime, codes: GpuBuffer, scales_biases: GpuBuffer, x_bf16:
               int(y_as_bf16))
 
 
+def embed_lookup_q4_mlx(rt: Runtime, bank: Q4MlxBank, token_ids: GpuBuffer, out: GpuBuffer, vocab: int, hidden: int,
+                        group_size: int, n_tokens: int) -> None:
+    """`nn::embed_lookup_q4_mlx` (src/nn.rs:3592-3658): gather dequantized rows; ids >= vocab give zeros."""
+    capi.call("tessl_embed_lookup_q4_mlx", rt.handle, bank.c(), token_ids.c(), out.c(), vocab, hidden, group_size,
+              n_tokens)
+
+
+def qwen35_rms_norm(rt: Runtime, x: GpuBuffer, w: GpuBuffer, out: GpuBuffer, out_as_bf16: bool, rows: int, dim: int,
+                    eps: float) -> None:
+    """`qwen35::rms_norm` (src/qwen35.rs:2654-2695): out = x * rsqrt(mean(x^2) + eps) * (1 + w)."""
+    capi.call("tessl_qwen35_rms_norm", rt.handle, x.c(), w.c(), out.c(), int(out_as_bf16), rows, dim, eps)
+
+
+def qwen35_residual_add(rt: Runtime, y: GpuBuffer, resid: GpuBuffer, rows: int, width: int) -> None:
+    """`qwen35::residual_add` for dense operands (src/qwen35.rs:2586-2623): resid += y."""
+    capi.call("tessl_qwen35_residual_add", rt.handle, y.c(), resid.c(), rows, width)
+
+
+def qwen35_add_rms_norm(rt: Runtime, y: GpuBuffer, resid: GpuBuffer, w: GpuBuffer, out: GpuBuffer, out_as_bf16: bool,
+                        rows: int, dim: int, eps: float) -> None:
+    """`qwen35::add_rms_norm` (src/qwen35.rs:2697-2747): the add and the norm in one launch."""
+    capi.call("tessl_qwen35_add_rms_norm", rt.handle, y.c(), resid.c(), w.c(), out.c(), int(out_as_bf16), rows, dim, eps)
+
+
 def q4_mlx_unpack(rt: Runtime, bank: Q4MlxBank, shape: QuantShape, out_u8: GpuBuffer) -> None:
     capi.call("tessl_q4_mlx_unpack", rt.handle, bank.c(), shape.c(), out_u8.c())
 

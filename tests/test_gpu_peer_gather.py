@@ -50,6 +50,37 @@ def test_refusals_and_single_rank_noop(rt):
     assert rt.take_dispatch_count() == 0
 
 
+def test_a_peer_that_never_arrives_poisons_the_runtime_and_nothing_else():
+    """A bounded device-side wait runs out: rank 0 of a two-rank exchange whose "peer" is a pair of local
+    buffers nobody signals. With the wait limit set to about a millisecond the kernel gives up, writes its
+    status word and returns; the call reports it, the runtime is poisoned and refuses further work, and a
+    fresh runtime on the same GPU works (the context is intact: nothing faulted or hung). The reference
+    reports a shared-event timeout the same way (src/runtime.rs:1498-1531, src/capi.rs:212-247)."""
+    import torch
+
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    r = nn.Runtime()
+    try:
+        bufs = [r.alloc_buffer(2 * 4096) for _ in range(2)]
+        flags = [r.buffer_from(np.zeros(32, np.uint32)) for _ in range(2)]
+        r.set_peer_wait_limit(2_000_000)  # clocks: ~1 ms
+        d = _desc(2, 0, 4096, [b.ptr for b in bufs], [f.ptr for f in flags])
+        with pytest.raises(capi.TesslError) as e:
+            capi.call("tessl_peer_gather", r.handle, ctypes.byref(d))
+        assert e.value.status == capi.TESSL_ERR
+        assert "gave up a bounded wait" in str(e.value) and "role 80" in str(e.value), str(e.value)  # 0x50
+        assert r.is_poisoned()
+        with pytest.raises(capi.TesslError, match="poisoned"):
+            r.alloc_buffer(16)
+    finally:
+        r.close()
+    with nn.Runtime() as fresh:
+        b = fresh.buffer_from(np.arange(64, dtype=np.uint32))
+        assert np.array_equal(b.read(np.uint32, 64), np.arange(64, dtype=np.uint32))
+        assert not fresh.is_poisoned()
+
+
 _CHILD = r"""
 import os, sys
 import numpy as np, torch, torch.distributed as dist
