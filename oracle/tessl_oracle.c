@@ -13,9 +13,12 @@
  *    right answer is.
  *  - "order-faithful" oracles, which follow the reference's *kernels*
  *    statement by statement (per-lane partial sums, the 16^k prescale, the
- *    simdgroup reduction), in f32. They are pinned against the known-answer
- *    words the reference's tests record for every kernel entry
- *    (tests/q4_kernels_template.rs:436-1494).
+ *    simdgroup reduction), in f32. They are pinned twice: against the
+ *    known-answer words the reference's tests record for every Q4 kernel entry
+ *    (tests/q4_kernels_template.rs:436-1494), and - Q8 included, for which the
+ *    reference recorded no vectors - bit for bit against the reference's own
+ *    kernel sources compiled for the CPU (`_ref/`, built by build.py from
+ *    ref_shim/; tests/test_oracle_ref.py).
  *
  * Every function cites the reference file:line it follows, by the file's path
  * inside the reference project.

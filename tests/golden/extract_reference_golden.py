@@ -6,7 +6,7 @@ eight output words) and writes the rows that pin the path built here to
 `q4_kernels_golden.json` beside this script. The rows were recorded by the
 reference's author from the kernels running on an Apple GPU.
 
-    python tests/golden/extract_reference_golden.py [/path/to/reference]
+    python tests/golden/extract_reference_golden.py /path/to/reference      (or TESSL_REFERENCE_ROOT=...)
 """
 import json
 import re
@@ -23,7 +23,12 @@ KEEP = {
 
 
 def main() -> None:
-    ref = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    import os
+
+    root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("TESSL_REFERENCE_ROOT")
+    if not root:
+        sys.exit("usage: extract_reference_golden.py <reference checkout>   (or set TESSL_REFERENCE_ROOT)")
+    ref = Path(root)
     text = (ref / "tests" / "q4_kernels_template.rs").read_text()
     body = text[text.index("const GOLDEN: &[Golden] = &["):]
     body = body[: body.index("\n];")]
