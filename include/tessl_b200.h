@@ -330,6 +330,58 @@ TESSL_API int32_t tessl_qwen35_add_rms_norm(TesslRuntime *rt, TesslBuf y, TesslB
                                   uint32_t out_as_bf16, uint32_t rows, uint32_t dim, float eps, char *err,
                                   size_t err_len);
 
+/* ------------------------------------------------- checkpoint -> bank --- */
+
+/* A safetensors file opened read-only (memory-mapped) with its header parsed
+ * and checked: every entry's dtype, shape and data_offsets agree, the ranges
+ * lie inside the file and do not overlap. Stands in for the safetensors crate
+ * behind `Loader::open` (src/loader.rs:33-118). Host only; NULL + err on refusal. */
+typedef struct TesslCheckpoint TesslCheckpoint;
+typedef struct TesslTensorInfo {
+    char dtype[8];      /* "U32", "BF16", "F32", ... as the header spells it */
+    uint32_t ndim;
+    uint64_t shape[8];
+    uint64_t nbytes;
+} TesslTensorInfo;
+
+TESSL_API TesslCheckpoint *tessl_checkpoint_open(const char *path, char *err, size_t err_len);
+TESSL_API void tessl_checkpoint_close(TesslCheckpoint *ck);
+TESSL_API int32_t tessl_checkpoint_tensor_count(const TesslCheckpoint *ck, uint64_t *out, char *err, size_t err_len);
+TESSL_API int32_t tessl_checkpoint_tensor_name(const TesslCheckpoint *ck, uint64_t index, char *name, size_t name_len,
+                                     char *err, size_t err_len);
+/* `Loader::tensor_info` (src/loader.rs:120-140): header facts, no bytes read. */
+TESSL_API int32_t tessl_checkpoint_tensor_info(const TesslCheckpoint *ck, const char *name, TesslTensorInfo *out, char *err,
+                                     size_t err_len);
+
+/* `MlxQuant::from_config_json` (src/qwen35_q4.rs:204-255): the `quantization`
+ * object of an mlx-lm config.json. Accepts only one uniform affine 4-bit
+ * group-64 quantization; a per-layer entry, another mode, width or group, or
+ * `quantization` and `quantization_config` that differ, are refused by name. */
+TESSL_API int32_t tessl_mlx_quant_from_config_json(const char *text, uint32_t *bits, uint32_t *group_size, char *err,
+                                         size_t err_len);
+
+/* `check_part` (src/qwen35_q4.rs:384-449): the three tensors of one quantized
+ * [rows, cols] matrix - `X.weight` U32 [rows, cols/8], `X.scales` and `X.biases`
+ * BF16 [rows, cols/64] - checked by their headers alone, before any allocation. */
+TESSL_API int32_t tessl_mlx_q4_check_part(const TesslCheckpoint *ck, const char *weight_name, uint64_t rows, uint64_t cols,
+                                char *err, size_t err_len);
+
+/* `Loader::mlx_q4_named` (src/loader.rs:256-318) into HOST memory: the parts'
+ * rows one after the other ([q; k; v], [gate; up]), packed words unchanged,
+ * scales and biases interleaved into bf16 (scale, bias) pairs; an infinite or
+ * NaN scale or bias is refused by tensor, element, row and group. Every part is
+ * checked before the first byte is written. */
+TESSL_API int32_t tessl_mlx_q4_read_bank(const TesslCheckpoint *ck, const char *const *weight_names, const uint64_t *rows,
+                               uint32_t nparts, uint64_t cols, void *packed, uint64_t packed_bytes, void *scales_biases,
+                               uint64_t scales_biases_bytes, char *err, size_t err_len);
+
+/* The same, into a bank whose device buffers the caller allocated (the
+ * reference allocates inside; here allocation stays with the host framework).
+ * Synchronises the runtime's stream before returning. */
+TESSL_API int32_t tessl_mlx_q4_load_bank(TesslRuntime *rt, const TesslCheckpoint *ck, const char *const *weight_names,
+                               const uint64_t *rows, uint32_t nparts, uint64_t cols, TesslQ4MlxBank bank, char *err,
+                               size_t err_len);
+
 /* ------------------------------------------------------- parity helpers --- */
 
 /* Debug kernels for the bit-exact parity gates: the bank's nibbles as one

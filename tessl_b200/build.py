@@ -17,7 +17,7 @@ from pathlib import Path
 HERE = Path(__file__).resolve().parent
 CSRC = HERE / "csrc"
 LIB = HERE / "_lib" / "libtessl_b200.so"
-SOURCES = ["capi.cu", "nn_q4.cu", "nn_q8.cu", "q4_weight.cu", "prefill_gemm.cu", "peer_gather.cu", "qwen35_norm.cu"]
+SOURCES = ["capi.cu", "nn_q4.cu", "nn_q8.cu", "q4_weight.cu", "prefill_gemm.cu", "peer_gather.cu", "qwen35_norm.cu", "mlx_q4_loader.cu"]
 
 
 def nvcc_path() -> str:

@@ -43,6 +43,10 @@ class QkvOutputs(C.Structure):
     _fields_ = [("q_out", Buf), ("k_out", Buf), ("v_out", Buf)]
 
 
+class TensorInfo(C.Structure):
+    _fields_ = [("dtype", C.c_char * 8), ("ndim", C.c_uint32), ("shape", C.c_uint64 * 8), ("nbytes", C.c_uint64)]
+
+
 class PeerGather(C.Structure):
     _fields_ = [("buffers", C.c_void_p * 8), ("flags", C.c_void_p * 8), ("rank", C.c_uint32), ("world", C.c_uint32),
                 ("bytes_per_rank", C.c_uint64)]
@@ -97,6 +101,17 @@ SIGNATURES = {
     "tessl_qwen35_rms_norm": (C.c_int32, [_RT, Buf, Buf, Buf, _u32, _u32, _u32, C.c_float] + _ERR),
     "tessl_qwen35_residual_add": (C.c_int32, [_RT, Buf, Buf, _u32, _u32] + _ERR),
     "tessl_qwen35_add_rms_norm": (C.c_int32, [_RT, Buf, Buf, Buf, Buf, _u32, _u32, _u32, C.c_float] + _ERR),
+    "tessl_checkpoint_open": (C.c_void_p, [C.c_char_p] + _ERR),
+    "tessl_checkpoint_close": (None, [C.c_void_p]),
+    "tessl_checkpoint_tensor_count": (C.c_int32, [C.c_void_p, C.POINTER(C.c_uint64)] + _ERR),
+    "tessl_checkpoint_tensor_name": (C.c_int32, [C.c_void_p, C.c_uint64, C.c_char_p, C.c_size_t] + _ERR),
+    "tessl_checkpoint_tensor_info": (C.c_int32, [C.c_void_p, C.c_char_p, C.POINTER(TensorInfo)] + _ERR),
+    "tessl_mlx_quant_from_config_json": (C.c_int32, [C.c_char_p, C.POINTER(_u32), C.POINTER(_u32)] + _ERR),
+    "tessl_mlx_q4_check_part": (C.c_int32, [C.c_void_p, C.c_char_p, C.c_uint64, C.c_uint64] + _ERR),
+    "tessl_mlx_q4_read_bank": (C.c_int32, [C.c_void_p, C.POINTER(C.c_char_p), C.POINTER(C.c_uint64), _u32, C.c_uint64,
+                                           C.c_void_p, C.c_uint64, C.c_void_p, C.c_uint64] + _ERR),
+    "tessl_mlx_q4_load_bank": (C.c_int32, [_RT, C.c_void_p, C.POINTER(C.c_char_p), C.POINTER(C.c_uint64), _u32, C.c_uint64,
+                                           Q4MlxBank] + _ERR),
     "tessl_q4_mlx_unpack": (C.c_int32, [_RT, Q4MlxBank, QuantShape, Buf] + _ERR),
     "tessl_q4_mlx_dequant": (C.c_int32, [_RT, Q4MlxBank, QuantShape, Buf] + _ERR),
 }
