@@ -12,19 +12,25 @@ step rotates over several layers' banks so the weight stream never fits L2.
 
 Printed: ONE JSON line. `value` is effective weight bandwidth (algorithmic
 weight bytes of the step / device time) with everything resident in HBM;
-`e2e` is the same through C-ABI calls with the activations copied from pinned
-host memory and the result read back every step (encode-only mode, the
-every-call-synchronous figure beside it); `roofline` describes the dominant
-kernel; `cpu_baseline` times the CPU oracle on the same workload. `extra` adds
-the single-GEMV target shape, the prefill GEMM and the other configurations.
-`clocks` are nvidia-smi samples taken while the timed graph keeps replaying for
-half a second after the timed replay (the timed region is shorter than one
-sampling period).
+`e2e` is the same measured by a compiled C++ host over the C ABI
+(tessl_b200/csrc/host_step_driver.cpp) with the activations copied from pinned
+host memory and the result read back every step (encode-only mode; the
+every-call-synchronous figure and the Python-ctypes figures beside it);
+`roofline` describes the dominant kernel, `roofline_prefill` the prefill GEMM;
+`cpu_baseline` times the CPU oracle on the same workload; `parity` is the GPU
+step's result against the CPU arm's on the same banks (layer 0 of the GPU arm
+is the CPU arm's layer). `extra` adds the LM head, small-batch, Q8 and prefill
+configurations. `clocks` are nvidia-smi samples taken while the timed graph
+keeps replaying for half a second after the timed replay (the timed region is
+shorter than one sampling period).
 
 With --gpus N > 1 (launched by torchrun, one rank per GPU) the large outputs
-(gate/up) are column-sharded over the ranks and all-gathered over NVLink by the
-library's peer-memory gather (NCCL if that is unavailable); q/k/v, o_proj and
-down are small and run replicated. Total work is fixed: "strong".
+(gate/up) are column-sharded over the ranks and the GEMV kernel itself stores
+each finished output into every rank's gather buffer over NVLink peer memory
+(an NCCL all-gather if peer memory is unavailable); q/k/v, o_proj and down are
+small and run replicated (the row-sharded down variant is timed beside it).
+`parity_n` says that every rank's gathered results equal the single-GPU
+operators' on the unsharded banks bit for bit. Total work is fixed: "strong".
 """
 from __future__ import annotations
 
@@ -65,22 +71,32 @@ def load_peaks():
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while a region runs."""
+    """Samples SM clocks and throttle reasons with nvidia-smi while a region runs. The GPU is named by
+    its UUID (an index would be wrong under CUDA_VISIBLE_DEVICES); `summary()` says so when no sample
+    could be taken."""
 
     Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
          "clocks_event_reasons.sw_power_cap")
 
-    def __init__(self, device: int):
-        self.device, self.rows, self.proc = device, [], None
+    def __init__(self, torch, device: int, enabled: bool = True):
+        self.rows, self.proc, self.enabled, self.why = [], None, enabled, ""
+        self.gpu = str(device)
+        try:
+            self.gpu = "GPU-" + str(torch.cuda.get_device_properties(device).uuid)
+        except Exception as e:  # noqa: BLE001
+            self.why = f"no UUID for device {device} ({type(e).__name__}); sampled by index"
 
     def __enter__(self):
+        if not self.enabled:
+            return self
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                                          "-lms", "100", "-i", str(self.device)], stdout=subprocess.PIPE, text=True)
+                                          "-lms", "100", "-i", self.gpu], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
             threading.Thread(target=self._read, daemon=True).start()
-        except OSError:
-            self.proc = None
+        except OSError as e:
+            self.proc, self.why = None, f"nvidia-smi did not start ({e})"
         return self
 
     def _read(self):
@@ -104,11 +120,24 @@ class ClockSampler:
                 if v.lower().startswith("active"):
                     reasons.add(n)
         if not sm:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
-        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+            return {"unavailable": self.why or f"nvidia-smi returned no sample for {self.gpu}", "samples": 0}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm),
+                "gpu": self.gpu}
 
 
 # --------------------------------------------------------------- CPU arm ---
+
+CPU_SEED = 0x7E550100  # the layer both arms share: the CPU arm's only layer, the GPU arm's layer 0
+
+
+def host_threads() -> int:
+    """Host cores this process may run on. Stated explicitly to the oracle: a launcher that sets
+    OMP_NUM_THREADS=1 for its ranks (torchrun does) would otherwise shrink the CPU arm to one thread."""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return max(1, os.cpu_count() or 1)
+
 
 def cpu_step_inputs(seed: int):
     """One layer's banks and activations as numpy arrays (seeded splitmix64)."""
@@ -153,9 +182,8 @@ def run_reference_arm(args, rank: int):
     so this is the CPU oracle port (oracle/tessl_oracle.c) with every host thread."""
     if rank != 0:
         return
-    from oracle import api
-    threads = api.max_threads()
-    banks, xs = cpu_step_inputs(0x7E550100)
+    threads = host_threads()
+    banks, xs = cpu_step_inputs(CPU_SEED)
     frac = 0.25  # a bounded sample: the leading quarter of every projection's rows
     for _ in range(max(1, args.warmup)):
         cpu_step(banks, xs, threads, frac)
@@ -194,35 +222,58 @@ def workload_config(n_gpus: int, layers: int = 4):
 # --------------------------------------------------------------- GPU arm ---
 
 class Layer:
-    """One layer's banks on this rank's GPU (sharded where the workload shards)."""
+    """One layer's banks on this rank's GPU: every bank unsharded, plus this rank's row slices of the
+    banks the workload shards (gate, up; down for the sharded-down variant)."""
 
-    def __init__(self, torch, nn, sharded, seed: int, world: int, rank: int):
+    def __init__(self, torch, nn, sharded, seed: int, world: int, rank: int, host_banks=None):
+        """`host_banks` (cpu_step_inputs' dict) makes this layer the very banks the CPU arm runs on;
+        without it the banks are drawn on the device (same distributions, all 32 bits of every word)."""
         self.keep = []
         gen = torch.Generator(device="cuda")
         gen.manual_seed(seed)
+        names = iter(("qkv", "o", "gate", "up", "down"))
+        B = nn.GpuBuffer.from_torch
 
         def bank(rows, cols):
-            packed = torch.randint(0, 2**31 - 1, (rows, cols // 8), dtype=torch.int32, device="cuda", generator=gen)
-            packed = packed * 2 + torch.randint(0, 2, packed.shape, dtype=torch.int32, device="cuda", generator=gen)
-            sc = (torch.rand((rows, cols // GROUP), device="cuda", generator=gen) * 0.018 + 0.002).to(torch.bfloat16)
-            bi = (-8.0 * sc.float() + 0.001 * torch.randn(sc.shape, device="cuda", generator=gen)).to(torch.bfloat16)
-            return packed, torch.stack([sc, bi], dim=-1).contiguous()
+            if host_banks is not None:
+                p, sb, r, c = host_banks[next(names)]
+                assert (r, c) == (rows, cols)
+                packed = torch.from_numpy(p.view(np.int32).reshape(rows, cols // 8)).cuda()
+                return packed, torch.from_numpy(sb.view(np.int16).reshape(rows, cols // GROUP, 2)).cuda().view(torch.bfloat16)
+            return device_bank(torch, gen, rows, cols)
 
-        def take(rows, cols, shard_it):
+        def take(rows, cols, shard_it, keep_full):
             packed, sb = bank(rows, cols)
             sh = sharded.make_shard(rows, world if shard_it else 1, rank if shard_it else 0)
+            full = None
+            if not (shard_it and world > 1) or keep_full:
+                self.keep += [packed, sb]
+                full = nn.Q4MlxBank(B(packed), B(sb))
+            local = full
             if shard_it and world > 1:
-                packed, sb = sharded.slice_bank(packed, sb, sh)
-            self.keep += [packed, sb]
-            return nn.Q4MlxBank(nn.GpuBuffer.from_torch(packed), nn.GpuBuffer.from_torch(sb)), sh
+                lp, lsb = sharded.slice_bank(packed, sb, sh)
+                self.keep += [lp, lsb]
+                local = nn.Q4MlxBank(B(lp), B(lsb))
+            return full, local, sh
 
-        self.qkv, _ = take(QKV, HIDDEN, False)
-        self.o, _ = take(HIDDEN, HIDDEN, False)
-        self.gate, self.sh_mid = take(INTER, HIDDEN, True)
-        self.up, _ = take(INTER, HIDDEN, True)
-        # down has a small output dimension (4096 rows): a slice of it is a few MB per GPU and its
-        # all-gather costs more than it saves, so it runs replicated like q/k/v and o.
-        self.down, self.sh_out = take(HIDDEN, INTER, False)
+        check = host_banks is not None  # the layer the N-GPU parity check runs on keeps its unsharded banks
+        self.qkv, _, _ = take(QKV, HIDDEN, False, True)
+        self.o, _, _ = take(HIDDEN, HIDDEN, False, True)
+        self.gate_full, self.gate, self.sh_mid = take(INTER, HIDDEN, True, check)
+        self.up_full, self.up, _ = take(INTER, HIDDEN, True, check)
+        # down (4096 output rows) runs replicated in the timed step; its row slice serves the
+        # sharded-down variant that is timed beside it
+        self.down, self.down_local, self.sh_down = take(HIDDEN, INTER, True, True)
+
+
+def device_bank(torch, gen, rows, cols):
+    """A bank drawn on the device: every bit of every packed word random, scale ~U(0.002, 0.02),
+    bias = -8 * scale + N(0, 0.001)."""
+    packed = torch.randint(0, 2**31 - 1, (rows, cols // 8), dtype=torch.int32, device="cuda", generator=gen)
+    packed = packed * 2 + torch.randint(0, 2, packed.shape, dtype=torch.int32, device="cuda", generator=gen)
+    sc = (torch.rand((rows, cols // GROUP), device="cuda", generator=gen) * 0.018 + 0.002).to(torch.bfloat16)
+    bi = (-8.0 * sc.float() + 0.001 * torch.randn(sc.shape, device="cuda", generator=gen)).to(torch.bfloat16)
+    return packed, torch.stack([sc, bi], dim=-1).contiguous()
 
 
 def run_ours(args, rank: int, world: int, local_rank: int):
@@ -238,22 +289,24 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     st = torch.cuda.ExternalStream(rt.stream, device=local_rank)
     peaks = load_peaks()
     n_layers = 4
-    layers = [Layer(torch, nn, sharded, 0x7E550000 + 97 * i, world, rank) for i in range(n_layers)]
+    # Layer 0 is the CPU arm's layer (same seeds, same generator); the others only have to keep the
+    # weight stream out of L2 and are drawn on the device.
+    cpu_inputs = cpu_step_inputs(CPU_SEED)
+    layers = [Layer(torch, nn, sharded, 0x7E550000 + 97 * i, world, rank, cpu_inputs[0] if i == 0 else None)
+              for i in range(n_layers)]
     dev = torch.device("cuda", local_rank)
-    gen = torch.Generator(device="cuda")
-    gen.manual_seed(0x7E55)
-    acts = {n: torch.randn(HIDDEN, device=dev, generator=gen).to(torch.bfloat16) for n in ("x_qkv", "x_o", "x_mlp")}
+    acts = {n: torch.from_numpy(v.view(np.int16)).to(dev).view(torch.bfloat16) for n, v in cpu_inputs[1].items()}
     qkv_out = torch.empty(QKV, device=dev)
     o_out = torch.empty(HIDDEN, device=dev)
-    # N > 1: the gathered gate/up output lives in peer-mapped memory and is exchanged by the
-    # library's own NVLink gather (a few KB per rank: an NCCL all-gather of that size measured
-    # ~14 us per call, more than the sharded GEMV before it); NCCL is the fallback if the
-    # peer-mapped allocation is unavailable.
-    peer = None
+    # N > 1: gate/up run on this rank's rows and the kernel itself stores every finished output into
+    # all ranks' gather buffers over NVLink (tessl_gemv_q4_mlx_gate_up_silu_sharded); NCCL is the
+    # fallback if the peer-mapped allocation is unavailable.
+    peer = peer_y = None
     if world > 1:
         why = ""
         try:
             peer = sharded.PeerGather(layers[0].sh_mid.local_rows * 2)
+            peer_y = sharded.PeerGather(sharded.slice_rows_per_rank(HIDDEN, world) * 4)
             probe = nn.Runtime(local_rank)  # a trial exchange on a runtime of its own: a failure poisons only that one
             try:
                 for _ in range(3):
@@ -265,7 +318,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         agreed = torch.tensor([1 if peer is not None else 0], device=dev)
         dist.all_reduce(agreed, op=dist.ReduceOp.MIN)
         if int(agreed.item()) == 0:
-            peer = None
+            peer = peer_y = None
             if rank == 0:
                 print(f"bench: peer-memory gather unavailable ({why or 'on another rank'}); using NCCL", file=sys.stderr)
     if peer is not None:
@@ -273,33 +326,35 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     else:
         mid_local = torch.empty(layers[0].sh_mid.local_rows, device=dev, dtype=torch.bfloat16)
         mid_full = torch.empty(INTER, device=dev, dtype=torch.bfloat16) if world > 1 else mid_local
-    y_local = torch.empty(layers[0].sh_out.local_rows, device=dev)
-    y_full = torch.empty(HIDDEN, device=dev) if layers[0].sh_out.world > 1 else y_local
+    y = torch.empty(HIDDEN, device=dev)
     B = nn.GpuBuffer.from_torch
     bufs = {k: B(v) for k, v in acts.items()}
-    qkv_b, o_b, midl_b, midf_b, yl_b = B(qkv_out), B(o_out), B(mid_local), B(mid_full), B(y_local)
+    qkv_b, o_b, midl_b, midf_b, y_b = B(qkv_out), B(o_out), B(mid_local), B(mid_full), B(y)
     sq = nn.QuantShape(QKV, HIDDEN, GROUP)
     so = nn.QuantShape(HIDDEN, HIDDEN, GROUP)
     sg = nn.QuantShape(layers[0].sh_mid.local_rows, HIDDEN, GROUP)
-    sd = nn.QuantShape(layers[0].sh_out.local_rows, INTER, GROUP)
-    launches_per_step = 4
+    sd = nn.QuantShape(HIDDEN, INTER, GROUP)
+    sd_local = nn.QuantShape(layers[0].sh_down.local_rows, INTER, GROUP)
+    launches_per_step = 4  # N > 1 with peer memory: still four, the exchange is inside the gate/up kernel
 
-    def step(i: int):
+    def step(i: int, down_sharded: bool = False):
         L = layers[i % n_layers]
         nn.gemv_q4_mlx_simd(rt, L.qkv, bufs["x_qkv"], qkv_b, sq)
         nn.gemv_q4_mlx_simd(rt, L.o, bufs["x_o"], o_b, so)
-        nn.gemv_q4_mlx_gate_up_silu(rt, L.gate, L.up, bufs["x_mlp"], midl_b, sg, True)
         if peer is not None:
-            peer.run(rt)
-        elif world > 1:
-            with torch.cuda.stream(st):
-                sharded.all_gather_rows(mid_local, L.sh_mid, out=mid_full)
-        nn.gemv_q4_mlx_simd(rt, L.down, midf_b, yl_b, sd)
-        if L.sh_out.world > 1:
-            with torch.cuda.stream(st):
-                sharded.all_gather_rows(y_local, L.sh_out, out=y_full)
-            return y_full
-        return y_local
+            peer.gate_up_silu(rt, L.gate, L.up, bufs["x_mlp"], sg, True)
+        else:
+            nn.gemv_q4_mlx_gate_up_silu(rt, L.gate, L.up, bufs["x_mlp"], midl_b, sg, True)
+            if world > 1:
+                with torch.cuda.stream(st):
+                    sharded.all_gather_rows(mid_local, L.sh_mid, out=mid_full)
+        if down_sharded and peer_y is not None:
+            # K = 12288 is outside the exchanging kernel's widths: the library runs the slice's GEMV and then
+            # the stand-alone exchange (two launches)
+            peer_y.gemv(rt, L.down_local, midf_b, sd_local)
+            return peer_y.full(torch.float32)
+        nn.gemv_q4_mlx_simd(rt, L.down, midf_b, y_b, sd)
+        return y
 
     def barrier():
         rt.synchronize()
@@ -310,43 +365,59 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     rt.set_encode_only(True)
     for i in range(max(args.warmup, 3)):
         step(i)
+        if peer_y is not None:
+            step(i, True)
     barrier()
 
-    # Launch-bound inner loop: one CUDA graph holds all K steps (kernels and, on
-    # several GPUs, the NCCL all-gathers, captured on the runtime's stream).
-    graph = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(graph, stream=st):
-        for i in range(args.steps):
-            step(i)
-    with torch.cuda.stream(st):
-        graph.replay()
-    barrier()
-
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    with ClockSampler(local_rank) as clocks:
-        barrier()
-        # The profiler range lets `ncu --profile-from-start off` list exactly the timed launches.
-        torch.cuda.profiler.start()
+    def timed_graph(down_sharded: bool, sample_clocks: bool):
+        # Launch-bound inner loop: one CUDA graph holds all K steps (kernels and, on the NCCL
+        # fallback, the all-gathers, captured on the runtime's stream).
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=st):
+            for i in range(args.steps):
+                step(i, down_sharded)
         with torch.cuda.stream(st):
-            e0.record(st)
             graph.replay()
-            e1.record(st)
         barrier()
-        torch.cuda.profiler.stop()
-        ms = e0.elapsed_time(e1)
-        if world > 1:
-            t = torch.tensor([ms], device=dev)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            ms = float(t.item())
-        # The timed region lasts a few milliseconds, less than one sampling period of nvidia-smi: the
-        # same graph keeps replaying (untimed, the same count on every rank) for about half a second
-        # so that the clock samples are taken under this very load.
-        with torch.cuda.stream(st):
-            for _ in range(min(5000, int(500.0 / max(ms, 1e-3)) + 1)):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with ClockSampler(torch, local_rank, enabled=sample_clocks) as clocks:
+            barrier()
+            # The profiler range lets `ncu --profile-from-start off` list exactly the timed launches.
+            torch.cuda.profiler.start()
+            with torch.cuda.stream(st):
+                e0.record(st)
                 graph.replay()
-        barrier()
-    ms_per_step = ms / args.steps
+                e1.record(st)
+            barrier()
+            torch.cuda.profiler.stop()
+            ms = e0.elapsed_time(e1)
+            if world > 1:
+                t = torch.tensor([ms], device=dev)
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+                ms = float(t.item())
+            if sample_clocks:
+                # The timed region lasts a few milliseconds, less than one sampling period of nvidia-smi: the
+                # same graph keeps replaying (untimed, the same count on every rank) for about half a second
+                # so that the clock samples are taken under this very load.
+                with torch.cuda.stream(st):
+                    for _ in range(min(5000, int(500.0 / max(ms, 1e-3)) + 1)):
+                        graph.replay()
+                barrier()
+        return ms / args.steps, clocks.summary()
+
+    ms_per_step, clocks = timed_graph(False, True)
     value = STEP_WEIGHT_BYTES / (ms_per_step * 1e-3) / 1e9
+    variants = None
+    if peer_y is not None:
+        ms_sharded_down, _ = timed_graph(True, False)
+        variants = {"down replicated (the timed step)": round(ms_per_step * 1e3, 3),
+                    "down row-sharded + exchange of its f32 outputs": round(ms_sharded_down * 1e3, 3), "unit": "us per step"}
+
+    # ---- parity, outside the timed region ----
+    rt.set_encode_only(False)
+    parity = check_parity(torch, dist, nn, rt, layers[0], cpu_inputs, step, bufs, mid_full, world, rank,
+                          peer_y is not None, dev)
+    rt.set_encode_only(True)
 
     # ---- per-projection device times (one graph per projection, same rotation) ----
     per_kernel = {}
@@ -379,7 +450,7 @@ def run_ours(args, rank: int, world: int, local_rank: int):
             "gate_up_silu 2x12288x4096": (lambda i: nn.gemv_q4_mlx_gate_up_silu(
                 rt, layers[i % n_layers].gate, layers[i % n_layers].up, bufs["x_mlp"], midl_b, sg, True),
                 2 * q4_weight_bytes(INTER, HIDDEN)),
-            "down 4096x12288": (lambda i: nn.gemv_q4_mlx_simd(rt, layers[i % n_layers].down, midf_b, yl_b, sd),
+            "down 4096x12288": (lambda i: nn.gemv_q4_mlx_simd(rt, layers[i % n_layers].down, midf_b, y_b, sd),
                                 q4_weight_bytes(HIDDEN, INTER)),
             "gemv 12288x4096 (target shape)": (lambda i: nn.gemv_q4_mlx_simd(
                 rt, layers[i % n_layers].gate, bufs["x_mlp"], gate_f32_b, nn.QuantShape(INTER, HIDDEN, GROUP)),
@@ -391,34 +462,82 @@ def run_ours(args, rank: int, world: int, local_rank: int):
                                 "frac_of_measured_hbm": round(nbytes / us / 1e3 / peaks["hbm_gbs"], 4)}
     rt.set_encode_only(False)
     return dict(torch=torch, dist=dist, nn=nn, rt=rt, st=st, layers=layers, acts=acts, step=step, ms_per_step=ms_per_step,
-                value=value, clocks=clocks.summary(), per_kernel=per_kernel, peaks=peaks, dev=dev,
-                launches_per_step=launches_per_step + (1 if peer is not None else 0), n_layers=n_layers,
-                y_local=y_local, bufs=bufs, gather="peer memory (tessl_peer_gather)" if peer is not None else "nccl")
+                value=value, clocks=clocks, per_kernel=per_kernel, peaks=peaks, dev=dev,
+                launches_per_step=launches_per_step, n_layers=n_layers, parity=parity, variants=variants,
+                y=y, bufs=bufs, cpu_inputs=cpu_inputs,
+                gather="peer memory, stores issued by the GEMV kernel (tessl_gemv_q4_mlx_gate_up_silu_sharded)"
+                if peer is not None else "nccl")
+
+
+def check_parity(torch, dist, nn, rt, L0, cpu_inputs, step, bufs, mid_full, world, rank, has_sharded_down, dev):
+    """Layer 0, outside the timed region. (1) The GPU step's y against the CPU arm's y on the same banks and
+    activations, within the stated tolerance (1e-2 relative + 2e-3 absolute after bf16 rounding of both).
+    (2) N > 1: on every rank the gathered gate/up output and y, in both down variants, against the single-GPU
+    operators on the unsharded banks, bit for bit (a row's summation order does not depend on the slice)."""
+    from tessl_b200 import synth
+    B = nn.GpuBuffer.from_torch
+    y_gpu = step(0).clone()
+    mid_gpu = mid_full.clone()
+    y_cpu, _ = cpu_step(cpu_inputs[0], cpu_inputs[1], host_threads(), 1.0)
+    rnd = lambda a: synth.bf16_bits_to_f32(synth.f32_to_bf16_bits(np.asarray(a, np.float32))).astype(np.float64)
+    g, w = rnd(y_gpu.cpu().numpy()), rnd(y_cpu)
+    err = np.abs(g - w)
+    bad = int(np.count_nonzero(err > 2e-3 + 1e-2 * np.abs(w)))
+    out = {"gpu_vs_cpu_y": "ok" if bad == 0 else f"{bad} of {w.size} outputs outside 1e-2 rel + 2e-3 abs",
+           "max_abs_err": float(err.max()), "layer": "layer 0: the CPU arm's banks and activations (tessl_b200/synth.py seeds)"}
+    if bad:
+        raise SystemExit(f"bench: the GPU step disagrees with the CPU arm: {out}")
+    if world > 1:
+        mid_ref = torch.empty(INTER, device=dev, dtype=torch.bfloat16)
+        y_ref = torch.empty(HIDDEN, device=dev)
+        nn.gemv_q4_mlx_gate_up_silu(rt, L0.gate_full, L0.up_full, bufs["x_mlp"], B(mid_ref), nn.QuantShape(INTER, HIDDEN, GROUP), True)
+        nn.gemv_q4_mlx_simd(rt, L0.down, B(mid_ref), B(y_ref), nn.QuantShape(HIDDEN, INTER, GROUP))
+        same = bool(torch.equal(mid_gpu.view(torch.int16)[:INTER], mid_ref.view(torch.int16))) and \
+            bool(torch.equal(y_gpu.view(torch.int32), y_ref.view(torch.int32)))
+        if has_sharded_down:
+            y2 = step(0, True).clone()
+            same = same and bool(torch.equal(y2.view(torch.int32)[:HIDDEN], y_ref.view(torch.int32)))
+        t = torch.tensor([1 if same else 0], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MIN)
+        out["parity_n"] = "ok" if int(t.item()) == 1 else "MISMATCH"
+        out["parity_n_what"] = ("gathered gate/up output and y" + (" (down replicated and down sharded)" if has_sharded_down else "")
+                                + f" on each of {world} ranks == single-GPU operators on the unsharded banks, bit for bit")
+        if out["parity_n"] != "ok":
+            raise SystemExit(f"bench: rank {rank}: sharded results differ from the single-GPU operators")
+    return out
 
 
 def measure_sharded_lm_head(ctx, args, world, rank):
-    """N > 1 only: the LM head (151936 x 4096, Q4 g64), rows sharded over the ranks, every rank
-    streaming its slice and one NCCL all-gather of the bf16 logits per call; device time of the
-    slowest rank, whole-job weight bytes per second."""
+    """N > 1 only: the LM head (151936 x 4096, Q4 g64), rows sharded over the ranks; every rank streams its
+    slice and the GEMV kernel itself stores the bf16 logits into all ranks' gather buffers (NCCL all-gather
+    on the fallback). Device time of the slowest rank, whole-job weight bytes per second. The launches rotate
+    over enough different slices that the stream exceeds L2 at every N; the first slice's gathered logits are
+    compared on every rank, bit for bit, with the single-GPU operator on the unsharded bank."""
     torch, dist, nn, rt, st = ctx["torch"], ctx["dist"], ctx["nn"], ctx["rt"], ctx["st"]
     from tessl_b200 import sharded
     rows, cols = 151936, HIDDEN
     sh = sharded.make_shard(rows, world, rank)
     per = sharded.slice_rows_per_rank(rows, world)
+    slice_bytes = q4_weight_bytes(per, cols)
+    nslices = max(2, -(-int(1.3 * 126e6) // slice_bytes))  # the rotation holds > 1.3 x L2
+    B = nn.GpuBuffer.from_torch
     gen = torch.Generator(device="cuda")
-    gen.manual_seed(0x7E55AA + rank)
-    banks, keep = [], []
-    for _ in range(2):  # two rotating slices: 2 x 350 MB / world, beyond L2 up to 4 ranks; smaller slices may sit in L2
-        packed = torch.randint(0, 2**31 - 1, (sh.local_rows, cols // 8), dtype=torch.int32, device="cuda", generator=gen)
-        sc = (torch.rand((sh.local_rows, cols // GROUP), device="cuda", generator=gen) * 0.018 + 0.002).to(torch.bfloat16)
-        sb = torch.stack([sc, (-8.0 * sc.float()).to(torch.bfloat16)], dim=-1).contiguous()
-        keep += [packed, sb]
-        banks.append(nn.Q4MlxBank(nn.GpuBuffer.from_torch(packed), nn.GpuBuffer.from_torch(sb)))
+    gen.manual_seed(0x7E55AA)  # the same on every rank: each draws the whole bank and keeps its rows
+    banks, keep, full0 = [], [], None
+    for i in range(nslices):
+        packed, sb = device_bank(torch, gen, rows, cols)
+        lp, lsb = sharded.slice_bank(packed, sb, sh)
+        keep += [lp, lsb]
+        banks.append(nn.Q4MlxBank(B(lp), B(lsb)))
+        if i == 0:
+            keep += [packed, sb]
+            full0 = nn.Q4MlxBank(B(packed), B(sb))
+        del packed, sb
     x = ctx["bufs"]["x_mlp"]
     peer = None
     if ctx.get("gather", "nccl") != "nccl":
         try:
-            peer = sharded.PeerGather(per * 2)
+            peer = sharded.PeerGather(-(-per * 2 // 16) * 16)
         except Exception:  # noqa: BLE001
             peer = None
         agreed = torch.tensor([1 if peer is not None else 0], device=ctx["dev"])
@@ -426,21 +545,37 @@ def measure_sharded_lm_head(ctx, args, world, rank):
         if int(agreed.item()) == 0:
             peer = None
     if peer is not None:
-        y_local, y_full = peer.local(torch.bfloat16), peer.full(torch.bfloat16)
+        y_full = peer.full(torch.bfloat16)
+        slot = peer.bytes_per_rank // 2
     else:
         y_local = torch.zeros(per, device=ctx["dev"], dtype=torch.bfloat16)
         y_full = torch.empty(per * world, device=ctx["dev"], dtype=torch.bfloat16)
-    yl_b = nn.GpuBuffer.from_torch(y_local)
+        yl_b = B(y_local)
+        slot = per
     shape = nn.QuantShape(sh.local_rows, cols, GROUP)
-    iters = 8
+    iters = 2 * nslices
 
     def call(i):
-        nn.gemv_q4_mlx_simd(rt, banks[i % 2], x, yl_b, shape, y_as_bf16=True)
         if peer is not None:
-            peer.run(rt)
+            peer.gemv(rt, banks[i % nslices], x, shape, y_as_bf16=True)
         else:
+            nn.gemv_q4_mlx_simd(rt, banks[i % nslices], x, yl_b, shape, y_as_bf16=True)
             with torch.cuda.stream(st):
                 dist.all_gather_into_tensor(y_full, y_local)
+
+    # parity first: slice 0 against the unsharded bank
+    call(0)
+    rt.synchronize()
+    torch.cuda.synchronize()
+    want = torch.empty(rows, device=ctx["dev"], dtype=torch.bfloat16)
+    nn.gemv_q4_mlx_simd(rt, full0, x, B(want), nn.QuantShape(rows, cols, GROUP), y_as_bf16=True)
+    got = torch.cat([y_full.view(world, slot)[r, : sharded.make_shard(rows, world, r).local_rows] for r in range(world)])
+    t = torch.tensor([1 if torch.equal(got.view(torch.int16), want.view(torch.int16)) else 0], device=ctx["dev"])
+    dist.all_reduce(t, op=dist.ReduceOp.MIN)
+    parity = "ok" if int(t.item()) == 1 else "MISMATCH"
+    if parity != "ok":
+        raise SystemExit(f"bench: rank {rank}: sharded LM-head logits differ from the single-GPU operator")
+    del full0, want
 
     rt.set_encode_only(True)
     for i in range(3):
@@ -469,17 +604,21 @@ def measure_sharded_lm_head(ctx, args, world, rank):
     us = float(t.item()) * 1e3
     nbytes = q4_weight_bytes(rows, cols)
     return {"us": round(us, 2), "weight_gbs": round(nbytes / us / 1e3, 1), "rows_per_gpu": int(sh.local_rows),
-            "how": "GEMV on this rank's row slice + one all-gather of the bf16 logits ("
-                   + ("peer memory" if peer is not None else "NCCL") + "), both in one CUDA graph"}
+            "slices_in_rotation": nslices, "rotation_mb_per_gpu": round(nslices * slice_bytes / 1e6, 1),
+            "parity_n": parity,
+            "how": "one launch per call: GEMV on this rank's row slice" + (
+                ", its reducer warps storing the bf16 logits into every rank's gather buffer over NVLink, one flag "
+                "exchange at the end" if peer is not None else " + one NCCL all-gather of the bf16 logits")
+                   + "; all calls in one CUDA graph"}, parity
 
 
-def measure_e2e(ctx, args):
-    """The same step through the C ABI with host buffers: activations copied from pinned host
-    memory each step and the down-projection output read back to the host each step. Timed in
-    the runtime's encode-only mode (the figure reported) and with every call synchronous."""
+def measure_e2e_python(ctx, args):
+    """The step through the C ABI from Python (ctypes): activations copied from pinned host memory each
+    step, the down projection's output read back each step. Timed in encode-only mode and with every
+    call synchronous. What an interpreter adds to the compiled host's figure."""
     torch, nn, rt = ctx["torch"], ctx["nn"], ctx["rt"]
     host_x = {k: v.view(torch.int16).cpu().pin_memory() for k, v in ctx["acts"].items()}
-    y = ctx["y_local"]
+    y = ctx["y"]
     host_y_t = torch.empty(y.numel(), dtype=torch.float32).pin_memory()
     host_y = host_y_t.numpy()  # pinned: the read-back is a plain DMA
     yb = nn.GpuBuffer(y.data_ptr(), y.numel() * 4, owner=y, rt=rt)
@@ -521,6 +660,48 @@ def measure_e2e(ctx, args):
             "value_every_call_synchronous": STEP_WEIGHT_BYTES / dt_sync / 1e9, "ms_per_step_synchronous": dt_sync * 1e3}
 
 
+def measure_e2e(ctx, args, device: int):
+    """End to end at one GPU: the compiled host (tessl_b200/csrc/host_step_driver.cpp, C++ over the public
+    header, built by tessl_b200/build.py) runs the same step with pinned host buffers; its figure is the one
+    reported, the Python-ctypes figure sits beside it. The driver builds its banks from the same seeds as
+    layer 0 here, and its first result is compared with this process's GPU result."""
+    import tempfile
+
+    from tessl_b200 import build as tb
+    py = measure_e2e_python(ctx, args)
+    steps = max(10, min(args.steps, 1000))
+    with tempfile.TemporaryDirectory(prefix="tessl_e2e_") as tmp:
+        y_path = os.path.join(tmp, "y.f32")
+        cmd = [str(tb.STEP_DRIVER), "--steps", str(steps), "--warmup", str(max(args.warmup, 3)), "--layers", str(ctx["n_layers"]),
+               "--seed", hex(CPU_SEED), "--device", str(device), "--y-out", y_path]
+        try:
+            r = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+            if r.returncode != 0:
+                raise RuntimeError(r.stderr.strip()[-400:] or f"exit code {r.returncode}")
+            d = json.loads(r.stdout.strip().splitlines()[-1])
+            y_drv = np.fromfile(y_path, dtype=np.float32)
+        except Exception as e:  # noqa: BLE001
+            py["host"] = "python ctypes"
+            py["compiled_host"] = {"unavailable": f"{type(e).__name__}: {e}"}
+            return py
+    ctx["rt"].set_encode_only(False)
+    y_py = ctx["step"](0).cpu().numpy()
+    same = bool(np.array_equal(y_drv.view(np.uint32), y_py.view(np.uint32)))
+    diff = float(np.abs(y_drv.astype(np.float64) - y_py.astype(np.float64)).max())
+    if not same and diff > 2e-3:
+        raise SystemExit(f"bench: the compiled host's step disagrees with this process's (max |diff| {diff})")
+    return {"value": d["value"], "unit": "GB/s", "h2d_bytes_per_step": d["h2d_bytes_per_step"],
+            "d2h_bytes_per_step": d["d2h_bytes_per_step"], "ms_per_step": d["ms_per_step"], "steps": d["steps"],
+            "host": "compiled C++ over include/tessl_b200.h (tessl_b200/csrc/host_step_driver.cpp), host clock around the steps",
+            "how": "per step: 3 host->device writes from pinned memory, 4 C-ABI operator calls, 1 device->host read of "
+                   "the result; writes and operators encoded without waiting (encode-only mode), the read waits",
+            "value_every_call_synchronous": d["value_every_call_synchronous"],
+            "ms_per_step_synchronous": d["ms_per_step_synchronous"],
+            "first_result_vs_this_process": "bit-exact" if same else f"max |diff| {diff:.3g}",
+            "python_ctypes": {k: py[k] for k in ("value", "ms_per_step", "value_every_call_synchronous",
+                                                 "ms_per_step_synchronous", "steps")}}
+
+
 def measure_extra(ctx, args):
     """Other configurations of the path, each timed on the device with CUDA events
     (single GPU): LM head, small-batch GEMM, MLX Q8 GEMV, and the Q4 prefill GEMM."""
@@ -531,10 +712,7 @@ def measure_extra(ctx, args):
     gen.manual_seed(0xC0FFEE)
 
     def rand_bank(rows, cols):
-        packed = torch.randint(0, 2**31 - 1, (rows, cols // 8), dtype=torch.int32, device=dev, generator=gen)
-        sc = (torch.rand((rows, cols // GROUP), device=dev, generator=gen) * 0.018 + 0.002).to(torch.bfloat16)
-        bi = (-8.0 * sc.float() + 0.001 * torch.randn(sc.shape, device=dev, generator=gen)).to(torch.bfloat16)
-        sb = torch.stack([sc, bi], dim=-1).contiguous()
+        packed, sb = device_bank(torch, gen, rows, cols)
         return (packed, sb), nn.Q4MlxBank(B(packed), B(sb))
 
     def timed(fn, nrot, iters):
@@ -608,11 +786,10 @@ def measure_extra(ctx, args):
     return out
 
 
-def cpu_baseline(args):
+def cpu_baseline(args, ctx_inputs=None):
     """The CPU oracle on full steps of the same workload, all host threads, for about ten seconds."""
-    from oracle import api
-    threads = api.max_threads()
-    banks, xs = cpu_step_inputs(0x7E550100)
+    threads = host_threads()
+    banks, xs = ctx_inputs if ctx_inputs is not None else cpu_step_inputs(CPU_SEED)
     cpu_step(banks, xs, threads, 0.1)
     t0 = time.perf_counter()
     done, steps = 0, 0
@@ -640,10 +817,7 @@ def run_case(spec: str):
     B = nn.GpuBuffer.from_torch
 
     def bank(rows, cols):
-        packed = torch.randint(0, 2**31 - 1, (rows, cols // 8), dtype=torch.int32, device="cuda", generator=gen)
-        sc = (torch.rand((rows, cols // GROUP), device="cuda", generator=gen) * 0.018 + 0.002).to(torch.bfloat16)
-        bi = (-8.0 * sc.float() + 0.001 * torch.randn(sc.shape, device="cuda", generator=gen)).to(torch.bfloat16)
-        sb = torch.stack([sc, bi], dim=-1).contiguous()
+        packed, sb = device_bank(torch, gen, rows, cols)
         return (packed, sb), nn.Q4MlxBank(B(packed), B(sb))
 
     if kind == "gemv":
@@ -703,7 +877,7 @@ def main():
         "scaling": "strong", "vs_baseline": None, "dtype": "f32 accumulate over bf16 x / Q4 weights", "data": "synthetic",
         "config": workload_config(world, ctx["n_layers"]),
         "gpu_launches": ctx["launches_per_step"] * args.steps, "gather": ctx.get("gather") if world > 1 else None,
-        "clocks": ctx["clocks"],
+        "clocks": ctx["clocks"], "parity": ctx["parity"],
         "frac_of_measured_hbm": round(ctx["value"] / (peaks["hbm_gbs"] * world), 4),
         "frac_of_nominal_8tbs": round(ctx["value"] / (8000.0 * world), 4),
     }
@@ -720,14 +894,28 @@ def main():
             # ncu: dram__bytes_read+write of one 12288x4096 launch was 28.35 MB for 28.31 MB algorithmic
             # (profiles/q4_gemv_mma_12288x4096.md): traffic = algorithmic bytes x 1.0013 per launch.
             "traffic": round(dom_bytes / 3 * 1.0013), "algorithmic_bytes_per_launch": dom_bytes // 3,
+            "traffic_source": "one ncu capture of a 12288x4096 launch (28.35 MB DRAM for 28.31 MB algorithmic), scaled by "
+                              "bytes to the mean of this step's three launches of the kernel",
             "launches_per_step": 3,
         }
         line["per_kernel"] = pk
-        line["e2e"] = measure_e2e(ctx, args)
+        line["e2e"] = measure_e2e(ctx, args, local_rank)
         if not args.no_extra:
             line["extra"] = measure_extra(ctx, args)
-        line["cpu_baseline"] = cpu_baseline(args)
+            pf = line["extra"].get("prefill_gemm 2048x12288x4096", {})
+            if "tflops" in pf:
+                # second roofline object: the prefill GEMM (tensor bound), timed alone, so against the burst peak
+                line["roofline_prefill"] = {
+                    "bound": "tensor", "kernel": "q4_prefill_gemm_pair_kernel<256>", "achieved": pf["tflops"],
+                    "peak": peaks["bf16_tflops"], "unit": "TFLOP/s", "frac": round(pf["tflops"] / peaks["bf16_tflops"], 4),
+                    "peak_source": peaks["source"] + " (burst: the kernel is timed alone)", "traffic": None,
+                    "flops_per_launch": 2 * 2048 * INTER * HIDDEN, "workload": "X[2048, 4096] bf16 x W[12288, 4096]^T Q4 g64, f32 out",
+                }
+        line["cpu_baseline"] = cpu_baseline(args, ctx["cpu_inputs"])
     else:
+        line["parity_n"] = ctx["parity"].get("parity_n")
+        if ctx["variants"]:
+            line["down_variants"] = ctx["variants"]
         # The headline figure is complete here. The two secondary measurements below and the closing
         # barrier involve further collectives; if one of them stalls or fails on some rank, the line is
         # still printed once (with the reason in place of the missing figure) and every rank leaves
@@ -753,7 +941,8 @@ def main():
         watchdog.start()
         try:
             # every rank copies its activations in and reads its result out; the slowest rank's time counts
-            e2e = measure_e2e(ctx, args)
+            e2e = measure_e2e_python(ctx, args)
+            e2e["host"] = "python ctypes (the compiled host drives one GPU)"
             torch = ctx["torch"]
             t = torch.tensor([e2e["ms_per_step"], e2e["ms_per_step_synchronous"]], device=ctx["dev"], dtype=torch.float64)
             ctx["dist"].all_reduce(t, op=ctx["dist"].ReduceOp.MAX)
@@ -762,8 +951,10 @@ def main():
             e2e["value_every_call_synchronous"] = STEP_WEIGHT_BYTES / (e2e["ms_per_step_synchronous"] * 1e-3) / 1e9
             e2e["how"] += f"; on each of the {world} ranks, slowest rank's time"
             line["e2e"] = e2e
-            sharded_head = measure_sharded_lm_head(ctx, args, world, rank)
+            sharded_head, head_parity = measure_sharded_lm_head(ctx, args, world, rank)
             line["extra"] = {f"lm_head 151936x4096 m=1 sharded over {world} GPUs": sharded_head}
+            if head_parity != "ok":
+                line["parity_n"] = head_parity
         except Exception as e:  # noqa: BLE001
             leave(f"{type(e).__name__}: {e}")
         print_line()

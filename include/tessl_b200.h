@@ -271,6 +271,27 @@ typedef struct TesslPeerGather {
 } TesslPeerGather;
 TESSL_API int32_t tessl_peer_gather(TesslRuntime *rt, const TesslPeerGather *gather, char *err, size_t err_len);
 
+/* tessl_gemv_q4_mlx_simd / tessl_gemv_q4_mlx_gate_up_silu on this rank's row slice
+ * of a column-sharded bank, with the exchange inside the GEMV kernel: NO
+ * COUNTERPART IN THE REFERENCE. `shape.rows` are the slice's rows; the f32 (or
+ * bf16) results go to byte offset rank * bytes_per_rank of EVERY rank's gather
+ * buffer - the warp that finishes an output row stores it locally and to each
+ * peer with plain NVLink stores - and the launch ends with one bounded flag
+ * exchange, after which buffers[rank] holds every rank's slice, as after
+ * tessl_peer_gather. One launch and one exposed flag round trip instead of two
+ * launches and two. Same descriptor, flag words and calling rules as
+ * tessl_peer_gather (every rank makes the matching call in the same order; the
+ * two kinds of call may be mixed on one descriptor); a rank whose slice is empty
+ * calls tessl_peer_gather instead. Shapes the tensor-core GEMV does not take
+ * (cols outside {1024, 2048, 4096}) run as the plain GEMV followed by
+ * tessl_peer_gather, with the same result. */
+TESSL_API int32_t tessl_gemv_q4_mlx_simd_sharded(TesslRuntime *rt, TesslQ4MlxBank bank, TesslBuf x_bf16,
+                                       const TesslPeerGather *gather, TesslQuantShape shape, uint32_t y_as_bf16,
+                                       char *err, size_t err_len);
+TESSL_API int32_t tessl_gemv_q4_mlx_gate_up_silu_sharded(TesslRuntime *rt, TesslQ4MlxBank gate, TesslQ4MlxBank up,
+                                               TesslBuf x_bf16, const TesslPeerGather *gather, TesslQuantShape shape,
+                                               uint32_t mid_as_bf16, char *err, size_t err_len);
+
 /* `Q4Weight::matmul` (src/qwen35_q4.rs:518-561): the M-dispatch policy over one
  * bank of group size 64. m == 0 is a no-op, 1 the GEMV, 2..=8 the small-batch
  * kernel, more the tensor-core GEMM (which refuses a residual). x is bf16

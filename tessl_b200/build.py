@@ -17,6 +17,7 @@ from pathlib import Path
 HERE = Path(__file__).resolve().parent
 CSRC = HERE / "csrc"
 LIB = HERE / "_lib" / "libtessl_b200.so"
+STEP_DRIVER = HERE / "_lib" / "tessl_step_driver"
 SOURCES = ["capi.cu", "nn_q4.cu", "nn_q8.cu", "q4_weight.cu", "prefill_gemm.cu", "peer_gather.cu", "qwen35_norm.cu", "mlx_q4_loader.cu"]
 
 
@@ -28,10 +29,10 @@ def nvcc_path() -> str:
 
 
 def is_stale() -> bool:
-    if not LIB.exists():
+    if not LIB.exists() or not STEP_DRIVER.exists():
         return True
-    t = LIB.stat().st_mtime
-    deps = list(CSRC.glob("*.cu")) + list(CSRC.glob("*.cuh")) + list(CSRC.glob("*.h"))
+    t = min(LIB.stat().st_mtime, STEP_DRIVER.stat().st_mtime)
+    deps = list(CSRC.glob("*.cu")) + list(CSRC.glob("*.cuh")) + list(CSRC.glob("*.h")) + list(CSRC.glob("*.cpp"))
     deps.append(HERE.parent / "include" / "tessl_b200.h")
     return any(d.stat().st_mtime > t for d in deps)
 
@@ -55,7 +56,21 @@ def build(force: bool = False, verbose_ptxas: bool = False) -> Path:
         raise RuntimeError("nvcc failed:\n$ " + " ".join(cmd) + "\n" + r.stdout + r.stderr)
     if verbose_ptxas:
         sys.stderr.write(r.stderr)
+    build_step_driver(host_cxx)
     return LIB
+
+
+def build_step_driver(host_cxx=None) -> Path:
+    """The compiled host of the end-to-end measurement (csrc/host_step_driver.cpp): plain C++ over the
+    public header, linked against the library beside it (found at run time through $ORIGIN)."""
+    cmd = [nvcc_path(), "-std=c++17", "-O2", "-o", str(STEP_DRIVER), str(CSRC / "host_step_driver.cpp"),
+           "-L", str(LIB.parent), "-ltessl_b200", "-Xlinker", "-rpath,$ORIGIN", "-Xcompiler", "-pthread"]
+    if host_cxx:
+        cmd += ["-ccbin", host_cxx]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError("step driver build failed:\n$ " + " ".join(cmd) + "\n" + r.stdout + r.stderr)
+    return STEP_DRIVER
 
 
 if __name__ == "__main__":

@@ -93,6 +93,9 @@ SIGNATURES = {
     "tessl_gemm_q4_mlx_tensorops_bf16": (C.c_int32, [_RT, Q4MlxBank, Buf, Buf, QuantShape, _u32] + _ERR),
     "tessl_gemm_q4_mlx_tensorops_noalloc": (C.c_int32, [_RT, Q4MlxBank, Buf, Buf, QuantShape, _u32] + _ERR),
     "tessl_peer_gather": (C.c_int32, [_RT, C.POINTER(PeerGather)] + _ERR),
+    "tessl_gemv_q4_mlx_simd_sharded": (C.c_int32, [_RT, Q4MlxBank, Buf, C.POINTER(PeerGather), QuantShape, _u32] + _ERR),
+    "tessl_gemv_q4_mlx_gate_up_silu_sharded": (C.c_int32, [_RT, Q4MlxBank, Q4MlxBank, Buf, C.POINTER(PeerGather), QuantShape,
+                                                           _u32] + _ERR),
     "tessl_q4_weight_matmul": (C.c_int32, [_RT, Q4MlxBank, _u32, _u32, Buf, _u32, Buf, C.POINTER(Buf)] + _ERR),
     "tessl_q4_weight_gate_up_silu": (C.c_int32, [_RT, Q4MlxBank, Q4MlxBank, _u32, _u32, Buf, Buf, _u32] + _ERR),
     "tessl_gemv_q8": (C.c_int32, [_RT, Buf, Buf, Buf, Buf, Buf, _u32, _u32, _u32] + _ERR),

@@ -460,6 +460,25 @@ int32_t tessl_peer_gather(TesslRuntime *rt, const TesslPeerGather *gather, char 
     });
 }
 
+int32_t tessl_gemv_q4_mlx_simd_sharded(TesslRuntime *rt, TesslQ4MlxBank bank, TesslBuf x_bf16, const TesslPeerGather *gather,
+                                       TesslQuantShape shape, uint32_t y_as_bf16, char *err, size_t err_len)
+{
+    return guarded(rt, err, err_len, true, [&]() -> tessl::Result {
+        if (!gather) return "gemv_q4_mlx_simd_sharded: null descriptor";
+        return tessl::nn::gemv_q4_mlx_simd_sharded(rt, bank, x_bf16, *gather, shape, y_as_bf16 != 0);
+    });
+}
+
+int32_t tessl_gemv_q4_mlx_gate_up_silu_sharded(TesslRuntime *rt, TesslQ4MlxBank gate, TesslQ4MlxBank up, TesslBuf x_bf16,
+                                               const TesslPeerGather *gather, TesslQuantShape shape, uint32_t mid_as_bf16,
+                                               char *err, size_t err_len)
+{
+    return guarded(rt, err, err_len, true, [&]() -> tessl::Result {
+        if (!gather) return "gemv_q4_mlx_gate_up_silu_sharded: null descriptor";
+        return tessl::nn::gemv_q4_mlx_gate_up_silu_sharded(rt, gate, up, x_bf16, *gather, shape, mid_as_bf16 != 0);
+    });
+}
+
 int32_t tessl_q4_weight_matmul(TesslRuntime *rt, TesslQ4MlxBank bank, uint32_t rows, uint32_t cols, TesslBuf x_bf16,
                                uint32_t m, TesslBuf y, const TesslBuf *resid, char *err, size_t err_len)
 {

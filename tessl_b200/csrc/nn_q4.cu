@@ -274,6 +274,16 @@ Result launch_mma_one(TesslRuntime *rt, const Q4GemvParams &p, int m, const MmaW
     mp.sb_pitch = w.sb_pitch ? w.sb_pitch : (p.cols >> p.group_shift) * 4;
     mp.x_pitch = w.x_pitch ? w.x_pitch : (Q8 ? p.cols >> 1 : p.cols);
     mp.status = rt->status_dev;
+    if (p.peer) {
+        const TesslPeerGather &g = *static_cast<const TesslPeerGather *>(p.peer);
+        if (BATCH || Q8 || p.nseg != 1) return "q4_gemv: a sharded launch has one bank (or one gate/up pair) and one row of x";
+        for (uint32_t r = 0; r < g.world; ++r) {
+            mp.peer.out[r] = static_cast<uint8_t *>(g.buffers[r]) + (size_t)g.rank * g.bytes_per_rank;
+            mp.peer.flags[r] = g.flags[r];
+        }
+        mp.peer.rank = g.rank, mp.peer.world = g.world;
+        mp.peer.wait_clocks = rt->peer_wait_clocks ? (long long)rt->peer_wait_clocks : kPeerWaitClocks;
+    }
     const uint32_t gpr = p.cols >> p.group_shift;
     const uint32_t part = BATCH ? q4m::kConsumers * 16 * 8 * 4 : q4m::kConsumers * 16 * 4;
     const uint32_t stage_bytes = 16 * ((p.cols >> 1) + q4m::kRowPad) + 16 * gpr * 4 + part;
@@ -370,6 +380,14 @@ bool tma_ok(const Q4GemvParams &p)
 /// summation order never depends on the launch) and the matching instantiation.
 Result launch_q4_gemv(TesslRuntime *rt, Q4GemvParams p, int m, int nb)
 {
+    if (p.peer && !(m == 1 && mma_ok(p))) {
+        // shapes the tensor-core kernel does not take: the slice by whichever kernel serves it, then the
+        // stand-alone exchange (same flag words, same result)
+        const TesslPeerGather *g = static_cast<const TesslPeerGather *>(p.peer);
+        p.peer = nullptr;
+        TESSL_TRY(launch_q4_gemv(rt, p, m, nb));
+        return nn::peer_gather(rt, *g);
+    }
     const uint32_t nchunks = std::max<uint32_t>(1u, (p.cols + q4k::kChunk - 1) / q4k::kChunk);
     if (m >= 1 && m <= 8 && (nb == 1 || m == 1) && mma_ok(p)) return launch_mma(rt, p, m, nb);
     {
@@ -563,6 +581,77 @@ Result gemv_q4_mlx_gate_up(TesslRuntime *rt, const char *entry, const char *what
     p.group_shift = log2_u32(shape.group_size);
     p.epi = silu ? EPI_GATE_UP_SILU : EPI_GATE_UP_GELU;
     p.out_bf16 = mid_as_bf16;
+    return launch_q4_gemv(rt, p, 1, 2);
+}
+
+/// This rank's slot of its own gather buffer, as the output buffer of a sharded launch.
+static Result sharded_out(const TesslPeerGather &g, const char *entry, uint64_t need_bytes, TesslBuf *out)
+{
+    TESSL_TRY(peer_gather_validate(g, entry));
+    if (need_bytes > g.bytes_per_rank)
+        return fmt("%s: the slice needs %llu bytes, the gather holds %llu per rank", entry, (unsigned long long)need_bytes,
+                   (unsigned long long)g.bytes_per_rank);
+    out->ptr = static_cast<uint8_t *>(g.buffers[g.rank]) + (size_t)g.rank * g.bytes_per_rank;
+    out->nbytes = g.bytes_per_rank;
+    return ok();
+}
+
+Result gemv_q4_mlx_simd_sharded(TesslRuntime *rt, const TesslQ4MlxBank &bank, const TesslBuf &x_bf16,
+                                const TesslPeerGather &gather, const TesslQuantShape &shape, bool y_as_bf16)
+{
+    const char *entry = "gemv_q4_mlx_simd_sharded";
+    TesslBuf y{};
+    TESSL_TRY(sharded_out(gather, entry, (uint64_t)shape.rows * (y_as_bf16 ? 2 : 4), &y));
+    if (shape.rows == 0) return fmt("%s: a rank with no rows takes part through tessl_peer_gather", entry);
+    TESSL_TRY(q4_bank_validate(bank, shape, entry));
+    TESSL_TRY(require(x_bf16, shape.cols, 2, std::string(entry) + " x_bf16"));
+    const Named writes[] = {{"gather slot", &y}};
+    const Named reads[] = {{"packed", &bank.packed}, {"scales_biases", &bank.scales_biases}, {"x_bf16", &x_bf16}};
+    TESSL_TRY(require_disjoint_writes(entry, writes, 1, reads, 3));
+    TESSL_TRY(check_alignment(bank, entry));
+    TESSL_TRY(require_aligned16(x_bf16, std::string(entry) + " x_bf16"));
+    Q4GemvParams p{};
+    p.seg[0] = make_seg(bank, nullptr, y, nullptr, shape.rows);
+    p.nseg = 1;
+    p.x = static_cast<const uint16_t *>(x_bf16.ptr);
+    p.cols = shape.cols;
+    p.group_shift = log2_u32(shape.group_size);
+    p.epi = EPI_STORE;
+    p.out_bf16 = y_as_bf16;
+    p.peer = gather.world > 1 ? &gather : nullptr;
+    return launch_q4_gemv(rt, p, 1, 1);
+}
+
+Result gemv_q4_mlx_gate_up_silu_sharded(TesslRuntime *rt, const TesslQ4MlxBank &gate, const TesslQ4MlxBank &up,
+                                        const TesslBuf &x, const TesslPeerGather &gather, const TesslQuantShape &shape,
+                                        bool mid_as_bf16)
+{
+    const char *entry = "gemv_q4_mlx_gate_up_silu_sharded";
+    TesslBuf mid{};
+    TESSL_TRY(sharded_out(gather, entry, (uint64_t)shape.rows * (mid_as_bf16 ? 2 : 4), &mid));
+    if (shape.rows == 0) return fmt("%s: a rank with no rows takes part through tessl_peer_gather", entry);
+    TESSL_TRY(q4_bank_validate(gate, shape, std::string(entry) + " gate"));
+    TESSL_TRY(q4_bank_validate(up, shape, std::string(entry) + " up"));
+    TESSL_TRY(require(x, shape.cols, 2, std::string(entry) + " x"));
+    const Named writes[] = {{"gather slot", &mid}};
+    const Named reads[] = {{"gate_packed", &gate.packed},
+                           {"gate_scales_biases", &gate.scales_biases},
+                           {"up_packed", &up.packed},
+                           {"up_scales_biases", &up.scales_biases},
+                           {"x", &x}};
+    TESSL_TRY(require_disjoint_writes(entry, writes, 1, reads, 5));
+    TESSL_TRY(check_alignment(gate, std::string(entry) + " gate"));
+    TESSL_TRY(check_alignment(up, std::string(entry) + " up"));
+    TESSL_TRY(require_aligned16(x, std::string(entry) + " x"));
+    Q4GemvParams p{};
+    p.seg[0] = make_seg(gate, &up, mid, nullptr, shape.rows);
+    p.nseg = 1;
+    p.x = static_cast<const uint16_t *>(x.ptr);
+    p.cols = shape.cols;
+    p.group_shift = log2_u32(shape.group_size);
+    p.epi = EPI_GATE_UP_SILU;
+    p.out_bf16 = mid_as_bf16;
+    p.peer = gather.world > 1 ? &gather : nullptr;
     return launch_q4_gemv(rt, p, 1, 2);
 }
 

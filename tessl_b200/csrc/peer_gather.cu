@@ -35,10 +35,6 @@ struct PeerGatherParams {
     uint32_t *status;
 };
 
-// Bound of every wait for a peer: ~0.5 s. The peers reach the same call within microseconds when they run
-// the same stream of work; a rank that is this late is treated as lost and the runtime is poisoned.
-constexpr long long kWaitClocks = 1000000000ll;
-
 __device__ __forceinline__ void st_release_sys(uint32_t *p, uint32_t v)
 {
     asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
@@ -112,20 +108,12 @@ namespace nn {
 
 Result peer_gather(TesslRuntime *rt, const TesslPeerGather &g)
 {
-    const char *what = "peer_gather";
-    if (g.world < 1 || g.world > 8) return fmt("%s: world %u is outside 1..8", what, g.world);
-    if (g.rank >= g.world) return fmt("%s: rank %u is outside world %u", what, g.rank, g.world);
-    if (g.bytes_per_rank % 16 != 0) return fmt("%s: bytes_per_rank %llu is not a multiple of 16", what,
-                                                (unsigned long long)g.bytes_per_rank);
-    for (uint32_t r = 0; r < g.world; ++r) {
-        if (!g.buffers[r] || !g.flags[r]) return fmt("%s: rank %u has a null buffer or flag pointer", what, r);
-        if (((uintptr_t)g.buffers[r] & 15u) != 0) return fmt("%s: rank %u's buffer is not 16-byte aligned", what, r);
-    }
+    TESSL_TRY(peer_gather_validate(g, "peer_gather"));
     if (g.world == 1 || g.bytes_per_rank == 0) return ok();
     PeerGatherParams p{};
     for (uint32_t r = 0; r < g.world; ++r) p.buf[r] = static_cast<uint8_t *>(g.buffers[r]), p.flags[r] = g.flags[r];
     p.rank = g.rank, p.world = g.world, p.bytes_per_rank = g.bytes_per_rank;
-    p.wait_clocks = rt->peer_wait_clocks ? (long long)rt->peer_wait_clocks : kWaitClocks;
+    p.wait_clocks = rt->peer_wait_clocks ? (long long)rt->peer_wait_clocks : kPeerWaitClocks;
     p.status = rt->status_dev;
     cudaLaunchConfig_t lc{};
     // one block per 32 KiB of slice, at most 16: a few KB go fastest from one block, the LM head's

@@ -61,6 +61,9 @@ struct Params {
     uint32_t group_shift;  // log2(group_size)
     int epi;
     int out_bf16;
+    // Host side only: the TesslPeerGather of a column-sharded launch whose kernel exchanges its own
+    // outputs (q4_gemv_mma.cuh), else null. Kernels other than that one never read it.
+    const void *peer;
 };
 
 constexpr int kChunk = 1024;  // columns one warp covers per step: 32 lanes x 32 nibbles

@@ -72,6 +72,16 @@ struct Seg {
     uint32_t rb_begin;  // first row block of this bank within the launch
 };
 
+/// Exchange of a column-sharded launch's outputs over NVLink peer memory (world <= 1: none). The
+/// flag words are those of peer_gather.cu: [0, 8) arrivals by source rank, [8, 16) completions by
+/// source rank, [16] this rank's call counter, [17] the ticket counter of the call's blocks.
+struct Peer {
+    uint8_t *out[8];     // where seg[0].out of THIS rank lives in rank r's gather buffer (out[rank] == seg[0].out)
+    uint32_t *flags[8];  // flag words of every rank
+    uint32_t rank, world;
+    long long wait_clocks;  // bound of every wait for a peer
+};
+
 struct Params {
     Seg seg[3];
     int nseg;
@@ -90,7 +100,40 @@ struct Params {
     uint32_t sb_pitch;
     uint32_t x_pitch;
     uint32_t *status;
+    Peer peer;
 };
+
+__device__ __forceinline__ void st_release_sys(uint32_t *p, uint32_t v)
+{
+    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t *p)
+{
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+/// Lane t < world (t != rank) of the calling warp waits until flag word `base + t` of this rank reaches
+/// `seq`; false (and a status word, role 0x50 like the stand-alone gather) when the bound runs out.
+__device__ __forceinline__ bool peer_wait(const Peer &pe, uint32_t *status, uint32_t base, uint32_t seq, uint32_t code)
+{
+    const uint32_t lane = threadIdx.x & 31;
+    bool ok_ = true;
+    if (lane < pe.world && lane != pe.rank) {
+        const uint32_t *f = pe.flags[pe.rank] + base + lane;
+        const long long t0 = clock64();
+        while ((int32_t)(ld_acquire_sys(f) - seq) < 0) {
+            if (clock64() - t0 > pe.wait_clocks) {
+                *(volatile uint32_t *)status = (0x50u << 24) | (code << 16) | lane;
+                ok_ = false;
+                break;
+            }
+            __nanosleep(64);
+        }
+    }
+    return __all_sync(0xffffffffu, ok_);
+}
 
 
 __device__ __forceinline__ uint2 lds64(uint32_t addr)
@@ -153,7 +196,9 @@ __global__ void __launch_bounds__(kThreads, TESSL_GEMV_MMA_MIN_BLOCKS) q4_gemv_m
     volatile int *abortp = &abort_flag;
     auto fail = [&](uint32_t role, uint32_t where) {
         *abortp = 1;
-        *(volatile uint32_t *)p.status = (0x40u << 24) | (role << 20) | (where & 0xfffffu);
+        // the first report stands: warps that leave because another one gave up do not overwrite its reason
+        if (*(volatile uint32_t *)p.status == 0)
+            *(volatile uint32_t *)p.status = (0x40u << 24) | (role << 20) | (where & 0xfffffu);
     };
     auto locate = [&](uint32_t rb, Seg &sg, uint32_t &row0) {
         int s = 0;
@@ -238,10 +283,25 @@ __global__ void __launch_bounds__(kThreads, TESSL_GEMV_MMA_MIN_BLOCKS) q4_gemv_m
     } else if (warp == kConsumers + 1) {
         // ------------------------------------------------ reducer ---
         asm volatile("griddepcontrol.wait;" ::: "memory");  // y and resid belong to the stream's order
+        // Sharded launch: the outputs also go to every peer's gather buffer, so this kernel is the
+        // exchange. Arrival first - this rank's earlier readers of its buffer precede this kernel in
+        // stream order, so "I am here" tells the peers they may overwrite it - then the stores as rows
+        // finish, then one completion handshake by the block that finishes last. The arrival round trip
+        // hides behind the weight stream; only the completion one is exposed.
+        const bool peered = !BATCH && p.peer.world > 1;
+        uint32_t seq = 0;
+        bool good = true;
+        if (peered) {
+            seq = *(volatile uint32_t *)(p.peer.flags[p.peer.rank] + 16) + 1;  // advanced by the call's last block only
+            if (blockIdx.x == 0 && (uint32_t)lane < p.peer.world && (uint32_t)lane != p.peer.rank)
+                st_release_sys(p.peer.flags[lane] + p.peer.rank, seq);
+            if (!peer_wait(p.peer, p.status, 0, seq, 3)) *abortp = 1, good = false;
+        }
         uint32_t s = 0, ph = 0;
-        for (uint32_t j = 0; j < n_local; ++j) {
+        for (uint32_t j = 0; good && j < n_local; ++j) {
             if (!mbar_wait(done(s), ph, abortp, 32)) {
                 if (lane == 0) fail(3, j);
+                good = false;
                 break;
             }
             Seg sg;
@@ -267,9 +327,18 @@ __global__ void __launch_bounds__(kThreads, TESSL_GEMV_MMA_MIN_BLOCKS) q4_gemv_m
                         v = dev::gelu_pytorch_tanh(v0) * v1;
                     }
                     if (p.out_bf16) {
-                        static_cast<uint16_t *>(sg.out)[row] = dev::f32_to_bf16_store(v);
+                        const uint16_t h = dev::f32_to_bf16_store(v);
+                        static_cast<uint16_t *>(sg.out)[row] = h;
+                        if (peered) {
+                            for (uint32_t r = 0; r < p.peer.world; ++r)
+                                if (r != p.peer.rank) reinterpret_cast<uint16_t *>(p.peer.out[r])[row] = h;
+                        }
                     } else {
                         static_cast<float *>(sg.out)[row] = v;
+                        if (peered) {
+                            for (uint32_t r = 0; r < p.peer.world; ++r)
+                                if (r != p.peer.rank) reinterpret_cast<float *>(p.peer.out[r])[row] = v;
+                        }
                     }
                 }
             } else {
@@ -303,6 +372,20 @@ __global__ void __launch_bounds__(kThreads, TESSL_GEMV_MMA_MIN_BLOCKS) q4_gemv_m
             __syncwarp();
             if (lane == 0) mbar_arrive(empty(s));  // partial sums read: the stage may be refilled
             if (++s == S) s = 0, ph ^= 1u;
+        }
+        if (peered && good) {
+            uint32_t *mine = p.peer.flags[p.peer.rank];
+            __threadfence_system();  // this block's peer stores, before its ticket
+            __syncwarp();
+            uint32_t ticket = 0;
+            if (lane == 0) ticket = atomicAdd(mine + 17, 1u);
+            ticket = __shfl_sync(0xffffffffu, ticket, 0);
+            if (ticket == gridDim.x - 1) {
+                __threadfence();  // the other blocks' stores (fenced before their tickets) precede the signal
+                if ((uint32_t)lane < p.peer.world && (uint32_t)lane != p.peer.rank)
+                    st_release_sys(p.peer.flags[lane] + 8 + p.peer.rank, seq);
+                if (peer_wait(p.peer, p.status, 8, seq, 4) && lane == 0) mine[17] = 0, mine[16] = seq;
+            }
         }
     } else {
         // ------------------------------------------------ consumers ---

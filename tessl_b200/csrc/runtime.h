@@ -216,6 +216,24 @@ inline Result require_i32_extent(uint64_t numel, const char *what)
     return ok();
 }
 
+// Bound of every wait for a peer GPU: ~0.5 s of SM clocks. The peers reach the same call within
+// microseconds when they run the same stream of work; a rank this late is treated as lost and the
+// runtime is poisoned. tessl_runtime_set_peer_wait_limit overrides it per runtime.
+constexpr long long kPeerWaitClocks = 1000000000ll;
+
+inline Result peer_gather_validate(const TesslPeerGather &g, const char *what)
+{
+    if (g.world < 1 || g.world > 8) return fmt("%s: world %u is outside 1..8", what, g.world);
+    if (g.rank >= g.world) return fmt("%s: rank %u is outside world %u", what, g.rank, g.world);
+    if (g.bytes_per_rank % 16 != 0)
+        return fmt("%s: bytes_per_rank %llu is not a multiple of 16", what, (unsigned long long)g.bytes_per_rank);
+    for (uint32_t r = 0; r < g.world; ++r) {
+        if (!g.buffers[r] || !g.flags[r]) return fmt("%s: rank %u has a null buffer or flag pointer", what, r);
+        if (((uintptr_t)g.buffers[r] & 15u) != 0) return fmt("%s: rank %u's buffer is not 16-byte aligned", what, r);
+    }
+    return ok();
+}
+
 #define TESSL_TRY(expr)                   \
     do {                                  \
         ::tessl::Result _r = (expr);      \
@@ -247,6 +265,11 @@ uint32_t gemm_q4_mlx_tensorops_max_k(uint32_t m, uint32_t n, uint32_t group_size
 Result gemm_q4_mlx_tensorops(TesslRuntime *rt, const TesslQ4MlxBank &bank, const TesslBuf &x_bf16,
                              const TesslBuf &y, const TesslQuantShape &shape, uint32_t m, OutKind out);
 Result peer_gather(TesslRuntime *rt, const TesslPeerGather &gather);
+Result gemv_q4_mlx_simd_sharded(TesslRuntime *rt, const TesslQ4MlxBank &bank, const TesslBuf &x_bf16,
+                                const TesslPeerGather &gather, const TesslQuantShape &shape, bool y_as_bf16);
+Result gemv_q4_mlx_gate_up_silu_sharded(TesslRuntime *rt, const TesslQ4MlxBank &gate, const TesslQ4MlxBank &up,
+                                        const TesslBuf &x_bf16, const TesslPeerGather &gather, const TesslQuantShape &shape,
+                                        bool mid_as_bf16);
 Result prefill_as_small_batches(TesslRuntime *rt, const TesslQ4MlxBank &bank, const TesslBuf &x_bf16, const TesslBuf &y,
                                 const TesslQuantShape &shape, uint32_t m, OutKind out, bool *handled);
 Result q8_mlx_mma(TesslRuntime *rt, const TesslBuf &codes, const TesslBuf &sb, const TesslBuf &x_bf16, const TesslBuf &y,

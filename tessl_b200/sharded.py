@@ -164,3 +164,21 @@ class PeerGather:
 
         from . import capi
         capi.call("tessl_peer_gather", rt.handle, ctypes.byref(self._desc))
+
+    def gemv(self, rt, bank, x_bf16, shape, y_as_bf16: bool = False) -> None:
+        """`tessl_gemv_q4_mlx_simd_sharded`: this rank's slice of W x computed and exchanged by one kernel;
+        afterwards `full(dtype)` holds every rank's slice."""
+        import ctypes
+
+        from . import capi
+        capi.call("tessl_gemv_q4_mlx_simd_sharded", rt.handle, bank.c(), x_bf16.c(), ctypes.byref(self._desc), shape.c(),
+                  1 if y_as_bf16 else 0)
+
+    def gate_up_silu(self, rt, gate, up, x_bf16, shape, mid_as_bf16: bool = True) -> None:
+        """`tessl_gemv_q4_mlx_gate_up_silu_sharded`: the fused gate/up projection on this rank's rows, exchanged
+        by the same kernel."""
+        import ctypes
+
+        from . import capi
+        capi.call("tessl_gemv_q4_mlx_gate_up_silu_sharded", rt.handle, gate.c(), up.c(), x_bf16.c(),
+                  ctypes.byref(self._desc), shape.c(), 1 if mid_as_bf16 else 0)
