@@ -37,7 +37,7 @@ def test_a_gate_up_bank_from_the_file_drives_the_fused_projection(rt, ckpt):
     nn.gemv_q4_mlx_simd(rt, both, xb, y, nn.QuantShape(2 * rows, cols, 64))
     got = y.read(np.float32, 2 * rows)
     for i, s in enumerate(("mlp.gate_proj", "mlp.up_proj")):
-        want = api.q4_dense_gemm(banks[s][0], banks[s][1], x, 1, rows, cols, 64)[0]
+        want = api.q4_dense_gemm(banks[s][0].view(np.uint8).reshape(-1), banks[s][1].reshape(-1), x, 1, rows, cols, 64)[0]
         assert_north_star(got[i * rows:(i + 1) * rows], want, s)
     # and the loaded halves, viewed as two banks, feed gate_up_silu
     gate = nn.Q4MlxBank(both.packed.view(0, rows * cols // 2), both.scales_biases.view(0, rows * (cols // 64) * 4))
