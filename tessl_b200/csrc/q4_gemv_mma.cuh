@@ -17,10 +17,13 @@
 // Structure (one persistent block per SM, 18 warps):
 //   warp 16   producer: streams row blocks (16 rows of one bank, or 8 + 8 rows of
 //             a gate/up pair) through a ring of stages with plain `cp.async.bulk`
-//             copies, one per row (each issued by its own lane) so that the rows
-//             sit 32 bytes past a multiple of 128 apart (bank-conflict-free reads),
-//             plus the rows' scale/bias pairs. It never waits for the preceding
-//             kernel: weights are not written by it.
+//             copies, one per PAIR of adjacent rows (each issued by its own lane): the
+//             copy engine's cost is per copy more than per byte (sixteen 2 KB copies per
+//             stage held a long stream to 0.75 of the HBM rate, eight 4 KB copies reach
+//             0.9). The pairs sit 32 bytes past a multiple of 128 apart
+//             (bank-conflict-free reads), and the two rows of a pair are the MMA rows g
+//             and g + 8 that one lane group reads. Plus the rows' scale/bias pairs.
+//             It never waits for the preceding kernel: weights are not written by it.
 //   warps 0-15 consumers: warp w owns columns [w K/16, (w+1) K/16) of every row.
 //             Its activations for that slice stay in registers as B fragments for
 //             the whole launch. Per stage it runs one MMA chain per quantization
@@ -170,6 +173,11 @@ __global__ void __launch_bounds__(kThreads, TESSL_GEMV_MMA_MIN_BLOCKS) q4_gemv_m
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t K = p.cols, gpr = K >> p.group_shift;
     const uint32_t row_bytes = K >> 1, pitch = row_bytes + kRowPad, sb_row_bytes = gpr * 4;
+    // MMA rows g and g + 8 (both read by lane group g) are two ADJACENT rows of a bank, 2 l and 2 l + 1, kept
+    // back to back in shared memory so that one bulk copy fetches both: the copy engine's cost is per
+    // copy more than per byte, and sixteen 2 KB copies per stage bounded the stream. Pairs sit 32 bytes
+    // past a multiple of 128 apart (bank-conflict-free fragment reads).
+    const uint32_t pair_pitch = 2 * row_bytes + kRowPad;
     const uint32_t part_bytes = BATCH ? kConsumers * 16 * 8 * 4 : kConsumers * 16 * 4;
     const uint32_t off_sb = 16 * pitch, off_part = off_sb + 16 * sb_row_bytes;
     const uint32_t stage_bytes = off_part + part_bytes;
@@ -218,10 +226,14 @@ __global__ void __launch_bounds__(kThreads, TESSL_GEMV_MMA_MIN_BLOCKS) q4_gemv_m
         // the 16 row slots of a stage, lanes 16 (and 17) the scale/bias rows of a bank.
         // Windowed rows (NB = 1 only): the scale/bias rows are not contiguous, lanes 16-31 fetch one each.
         const bool sb_by_row = NB == 1 && p.sb_pitch != sb_row_bytes;
-        const uint32_t my_bank = lane < 16 ? (uint32_t)lane / RPB : (sb_by_row ? 0u : (uint32_t)lane - 16);
-        const uint32_t my_r = lane < 16 ? (uint32_t)lane % RPB : (sb_by_row ? (uint32_t)lane - 16 : 0u);
+        const bool pair_copy = p.row_pitch == row_bytes;  // dense rows: two adjacent rows are one contiguous range
+        constexpr uint32_t HP = RPB / 2;                  // row pairs per bank and stage
+        // lane m < 16 owns MMA row m: lane group g = m % 8, upper half hi = m / 8 -> bank g / HP, local row 2 (g % HP) + hi
+        const uint32_t mg = (uint32_t)lane & 7u, mhi = ((uint32_t)lane >> 3) & 1u;
+        const uint32_t my_bank = lane < 16 ? mg / HP : (sb_by_row ? 0u : (uint32_t)lane - 16);
+        const uint32_t my_r = lane < 16 ? 2 * (mg % HP) + mhi : (sb_by_row ? (uint32_t)lane - 16 : 0u);
         const bool copies = sb_by_row || lane < 16 + NB;
-        const uint32_t my_dst = lane < 16 ? (uint32_t)lane * pitch
+        const uint32_t my_dst = lane < 16 ? mg * pair_pitch + mhi * row_bytes
                                           : off_sb + (sb_by_row ? my_r : my_bank * RPB) * sb_row_bytes;
         uint32_t s = 0, ph = 0, issued = 0;
         int cur_seg = -1;
@@ -264,6 +276,8 @@ __global__ void __launch_bounds__(kThreads, TESSL_GEMV_MMA_MIN_BLOCKS) q4_gemv_m
                     } else if (my_r < nrows) {
                         bulk_g2s(st + my_dst, src, sb_row_bytes, full(s));
                     }
+                } else if (pair_copy) {
+                    if (mhi == 0 && my_r < nrows) bulk_g2s(st + my_dst, src, my_r + 1 < nrows ? 2 * row_bytes : row_bytes, full(s));
                 } else if (my_r < nrows) {
                     bulk_g2s(st + my_dst, src, row_bytes, full(s));
                 }
@@ -312,10 +326,12 @@ __global__ void __launch_bounds__(kThreads, TESSL_GEMV_MMA_MIN_BLOCKS) q4_gemv_m
                 // lane r < RPB: output row row0 + r (for a gate/up pair also its up partner, MMA row r + 8)
                 if (lane < RPB && row0 + lane < sg.rows) {
                     float v0 = 0.0f, v1 = 0.0f;
+                    // local row l sits in MMA row (l odd ? 8 : 0) + l / 2; its up partner RPB / 2 rows further
+                    const uint32_t mrow = (((uint32_t)lane & 1u) << 3) + ((uint32_t)lane >> 1);
 #pragma unroll
                     for (int w = 0; w < kConsumers; ++w) {
-                        v0 += __uint_as_float(lds32(part + (w * 16 + lane) * 4));
-                        if (NB == 2) v1 += __uint_as_float(lds32(part + (w * 16 + lane + 8) * 4));
+                        v0 += __uint_as_float(lds32(part + (w * 16 + mrow) * 4));
+                        if (NB == 2) v1 += __uint_as_float(lds32(part + (w * 16 + mrow + RPB / 2) * 4));
                     }
                     const uint32_t row = row0 + lane;
                     float v = v0;
@@ -351,7 +367,7 @@ __global__ void __launch_bounds__(kThreads, TESSL_GEMV_MMA_MIN_BLOCKS) q4_gemv_m
                     v[0] += __uint_as_float(q.x), v[1] += __uint_as_float(q.y);
                     v[2] += __uint_as_float(q.z), v[3] += __uint_as_float(q.w);
                 }
-                const uint32_t row = row0 + r;
+                const uint32_t row = row0 + 2 * (r & 7u) + (r >> 3);  // MMA row r holds local row 2 (r % 8) + r / 8
                 if (row < sg.rows) {
 #pragma unroll
                     for (int c = 0; c < 4; ++c) {
@@ -527,8 +543,8 @@ __global__ void __launch_bounds__(kThreads, TESSL_GEMV_MMA_MIN_BLOCKS) q4_gemv_m
                 break;
             }
             const uint32_t st = ring + s * stage_bytes;
-            const uint32_t row_lo = st + g * pitch + w_off, row_hi = row_lo + 8 * pitch;
-            const uint32_t sb_lo = st + off_sb + g * sb_row_bytes + sb_off, sb_hi = sb_lo + 8 * sb_row_bytes;
+            const uint32_t row_lo = st + g * pair_pitch + w_off, row_hi = row_lo + row_bytes;
+            const uint32_t sb_lo = st + off_sb + 2 * g * sb_row_bytes + sb_off, sb_hi = sb_lo + sb_row_bytes;
             float dlo[NGS], dhi[NGS];        // M = 1: dot of MMA rows g and g + 8 per group
             // BATCH: rows g, g + 8 x columns 2 t, 2 t + 1, one accumulator per group class jj % 4 so that
             // the sum is formed in the same order as in the M = 1 path (where lane t of a quad takes
