@@ -25,11 +25,11 @@ using q4k::EPI_STORE;
 using Q4Seg = q4k::Seg;
 using Q4GemvParams = q4k::Params;
 
-__global__ void swiglu_kernel(const float *gate, const float *up, void *out, uint32_t n, int out_bf16)
+__global__ void swiglu_kernel(const float *gate, const float *up, void *out, uint32_t n, int out_bf16, int gelu)
 {
     const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
-    const float v = dev::silu(gate[i]) * up[i];
+    const float v = (gelu ? dev::gelu_pytorch_tanh(gate[i]) : dev::silu(gate[i])) * up[i];
     if (out_bf16) {
         static_cast<uint16_t *>(out)[i] = dev::f32_to_bf16_store(v);
     } else {
@@ -254,11 +254,15 @@ struct MmaWindow {
     uint32_t row_pitch = 0, sb_pitch = 0, x_pitch = 0;
 };
 
-template <int SW, int WPG, int NB, bool BATCH, bool Q8 = false>
+/// Shared memory one block of the tensor-core GEMV may use: the per-block maximum of sm_100 less the kernel's few
+/// static bytes.
+constexpr uint32_t kMmaSmemBudget = 232448u - 512u;
+
+template <int SW, int WPG, int NB, bool BATCH, bool Q8 = false, int NWIN = 1, int ROWS = 16>
 Result launch_mma_one(TesslRuntime *rt, const Q4GemvParams &p, int m, const MmaWindow &w = MmaWindow{})
 {
-    auto kernel = q4m::q4_gemv_mma_kernel<SW, WPG, NB, BATCH, Q8>;
-    constexpr uint32_t RPB = 16 / NB;
+    auto kernel = q4m::q4_gemv_mma_kernel<SW, WPG, NB, BATCH, Q8, NWIN, ROWS>;
+    constexpr uint32_t RPB = ROWS / NB;
     q4m::Params mp{};
     uint32_t rb = 0;
     for (int s = 0; s < p.nseg; ++s) {
@@ -286,9 +290,10 @@ Result launch_mma_one(TesslRuntime *rt, const Q4GemvParams &p, int m, const MmaW
     }
     const uint32_t gpr = p.cols >> p.group_shift;
     const uint32_t part = BATCH ? q4m::kConsumers * 16 * 8 * 4 : q4m::kConsumers * 16 * 4;
-    const uint32_t stage_bytes = 16 * ((p.cols >> 1) + q4m::kRowPad) + 16 * gpr * 4 + part;
-    const uint32_t x_stage = 16 + q4m::kConsumers * q4m::kXStageBytes;  // the warps' staged slices of x (M = 1)
-    uint32_t stages = std::min<uint32_t>(8u, (216u * 1024u - x_stage) / (stage_bytes + 24));
+    const uint32_t stage_bytes = ROWS * ((p.cols >> 1) + q4m::kRowPad) + ROWS * gpr * 4 + part;
+    const uint32_t x_stage = 16 + q4m::kConsumers * q4m::kXStageBytes * NWIN;  // the warps' staged slices of x (M = 1)
+    uint32_t stages = std::min<uint32_t>(8u, (kMmaSmemBudget - x_stage) / (stage_bytes + 24));
+    if (stages < 2) return "q4_gemv_mma: the ring does not fit two stages";
     mp.stages = stages;
     const size_t smem = (size_t)stages * (stage_bytes + 24) + x_stage;
     TESSL_TRY(smem_opt_in(rt, reinterpret_cast<const void *>(kernel), smem, "q4_gemv_mma: shared memory opt-in", true));
@@ -328,6 +333,35 @@ Result launch_mma(TesslRuntime *rt, const Q4GemvParams &p, int m, int nb, const 
     }
     if (wpg == 1) return launch_mma_sw<2, 1>(rt, p, m, nb, w);
     return launch_mma_sw<2, 2>(rt, p, m, nb, w);
+}
+
+/// One row of x over rows of 8192 or 12288 columns (a 4096 x 12288 down projection): the tensor-core kernel
+/// with every stage holding whole long rows, the warps walking the 4096-column windows inside it. Two
+/// stages fit in shared memory (of 16 rows at 8192 columns, of 14 at 12288). Taken for every M = 1 form at
+/// these widths, whatever the row count, so that a row's summation order still depends on K and G alone.
+bool mma_long_ok(const Q4GemvParams &p, int m)
+{
+    if (!mma_enabled() || m != 1) return false;
+    if (p.cols != 8192 && p.cols != 12288) return false;
+    if (p.group_shift < 5 || p.group_shift > 7) return false;
+    for (int s = 0; s < p.nseg; ++s) {
+        const Q4Seg &a = p.seg[s];
+        if (((uintptr_t)a.sb0 & 15u) || (a.sb1 && ((uintptr_t)a.sb1 & 15u))) return false;
+    }
+    return true;
+}
+
+Result launch_mma_long(TesslRuntime *rt, const Q4GemvParams &p)
+{
+    const int wpg = 1 << (p.group_shift - 5);
+    if (p.cols == 8192) {
+        if (wpg == 1) return launch_mma_one<8, 1, 1, false, false, 2, 16>(rt, p, 1);
+        if (wpg == 2) return launch_mma_one<8, 2, 1, false, false, 2, 16>(rt, p, 1);
+        return launch_mma_one<8, 4, 1, false, false, 2, 16>(rt, p, 1);
+    }
+    if (wpg == 1) return launch_mma_one<8, 1, 1, false, false, 3, 14>(rt, p, 1);
+    if (wpg == 2) return launch_mma_one<8, 2, 1, false, false, 3, 14>(rt, p, 1);
+    return launch_mma_one<8, 4, 1, false, false, 3, 14>(rt, p, 1);
 }
 
 /// Batches of 3..8 rows over rows longer than the tensor-core kernel's 4096 columns (a 12288-column
@@ -380,7 +414,7 @@ bool tma_ok(const Q4GemvParams &p)
 /// summation order never depends on the launch) and the matching instantiation.
 Result launch_q4_gemv(TesslRuntime *rt, Q4GemvParams p, int m, int nb)
 {
-    if (p.peer && !(m == 1 && mma_ok(p))) {
+    if (p.peer && !(m == 1 && (mma_ok(p) || (mma_long_ok(p, m) && nb == 1)))) {
         // shapes the tensor-core kernel does not take: the slice by whichever kernel serves it, then the
         // stand-alone exchange (same flag words, same result)
         const TesslPeerGather *g = static_cast<const TesslPeerGather *>(p.peer);
@@ -390,6 +424,35 @@ Result launch_q4_gemv(TesslRuntime *rt, Q4GemvParams p, int m, int nb)
     }
     const uint32_t nchunks = std::max<uint32_t>(1u, (p.cols + q4k::kChunk - 1) / q4k::kChunk);
     if (m >= 1 && m <= 8 && (nb == 1 || m == 1) && mma_ok(p)) return launch_mma(rt, p, m, nb);
+    if (mma_long_ok(p, m)) {
+        // The kernel takes one bank per launch at these widths. The bank-routed forms run as one launch per
+        // bank, the gate/up forms as two launches into scratch and the activation kernel: what the fused
+        // launches are defined to equal bit for bit.
+        if (nb == 1) {
+            for (int sidx = 0; sidx < p.nseg; ++sidx) {
+                Q4GemvParams q = p;
+                q.seg[0] = p.seg[sidx], q.nseg = 1;
+                TESSL_TRY(launch_mma_long(rt, q));
+            }
+            return ok();
+        }
+        const uint32_t rows = p.seg[0].rows;
+        void *tmp = nullptr;
+        TESSL_TRY(scratch_reserve(rt, (size_t)rows * 8, &tmp));
+        float *g = static_cast<float *>(tmp), *u = g + rows;
+        Q4GemvParams q = p;
+        q.epi = EPI_STORE, q.out_bf16 = 0, q.peer = nullptr;
+        q.seg[0].packed1 = nullptr, q.seg[0].sb1 = nullptr, q.seg[0].out = g;
+        TESSL_TRY(launch_mma_long(rt, q));
+        q.seg[0].packed0 = p.seg[0].packed1, q.seg[0].sb0 = p.seg[0].sb1, q.seg[0].out = u;
+        TESSL_TRY(launch_mma_long(rt, q));
+        swiglu_kernel<<<(rows + 255) / 256, 256, 0, rt->stream>>>(g, u, p.seg[0].out, rows, p.out_bf16,
+                                                                  p.epi == EPI_GATE_UP_GELU ? 1 : 0);
+        rt->dispatch_count += 1;
+        TESSL_TRY(cuda_check(rt, cudaGetLastError(), "gate/up activation launch"));
+        if (p.peer) return nn::peer_gather(rt, *static_cast<const TesslPeerGather *>(p.peer));
+        return ok();
+    }
     {
         Result res = ok();
         if (launch_mma_windows(rt, p, m, nb, res)) return res;
@@ -750,7 +813,7 @@ Result swiglu(TesslRuntime *rt, const TesslBuf &gate, const TesslBuf &up, const 
     if (n == 0) return ok();
     swiglu_kernel<<<(n + 255) / 256, 256, 0, rt->stream>>>(static_cast<const float *>(gate.ptr),
                                                           static_cast<const float *>(up.ptr), out.ptr, n,
-                                                          out_as_bf16 ? 1 : 0);
+                                                          out_as_bf16 ? 1 : 0, 0);
     rt->dispatch_count += 1;
     return cuda_check(rt, cudaGetLastError(), "swiglu launch");
 }

@@ -160,12 +160,19 @@ __device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1
 /// Q8: the rows hold 8-bit codes. A code c = 16 h + l is taken as its two nibbles l, h against the
 ///     activations x and 16 x (exact in bf16), so a row of K codes runs as a row of 2 K nibbles:
 ///     `cols` and the group size are given in nibbles (2 K, 2 G), x has cols / 2 elements per row.
-template <int SW, int WPG, int NB, bool BATCH, bool Q8 = false>
+/// NWIN: windows of 512 SW columns a row consists of (M = 1, one bank): rows of 8192 or 12288 columns run as
+///     2 or 3 windows inside every stage, each warp taking its slice of every window in turn, so that a
+///     long-row projection is still one launch with one fixed part.
+/// ROWS: rows per stage (16, or 14 where two stages of 16 long rows would not fit in shared memory; the
+///     MMA's unused rows cost nothing that matters: the kernel is bound by the weight stream).
+template <int SW, int WPG, int NB, bool BATCH, bool Q8 = false, int NWIN = 1, int ROWS = 16>
 __global__ void __launch_bounds__(kThreads, TESSL_GEMV_MMA_MIN_BLOCKS) q4_gemv_mma_kernel(const Params p)
 {
     asm volatile("griddepcontrol.launch_dependents;");
+    static_assert(NWIN == 1 || (NB == 1 && !BATCH && !Q8), "windows: one bank, one row of x, Q4");
+    static_assert(ROWS % (2 * NB) == 0 && ROWS <= 16, "whole row pairs per bank");
     constexpr int NGS = SW / WPG;     // groups per slice
-    constexpr int RPB = 16 / NB;      // rows per bank and stage
+    constexpr int RPB = ROWS / NB;    // rows per bank and stage
     constexpr int NQ = (NGS + 3) / 4;  // affine groups per lane when M = 1
     static_assert(SW % WPG == 0 && NGS >= 1, "a warp's slice holds whole groups");
     extern __shared__ __align__(128) uint8_t smem[];
@@ -179,7 +186,7 @@ __global__ void __launch_bounds__(kThreads, TESSL_GEMV_MMA_MIN_BLOCKS) q4_gemv_m
     // past a multiple of 128 apart (bank-conflict-free fragment reads).
     const uint32_t pair_pitch = 2 * row_bytes + kRowPad;
     const uint32_t part_bytes = BATCH ? kConsumers * 16 * 8 * 4 : kConsumers * 16 * 4;
-    const uint32_t off_sb = 16 * pitch, off_part = off_sb + 16 * sb_row_bytes;
+    const uint32_t off_sb = (ROWS / 2) * 2 * pitch, off_part = off_sb + ROWS * sb_row_bytes;
     const uint32_t stage_bytes = off_part + part_bytes;
     const uint32_t S = p.stages;
     const uint32_t ring = smem_u32(smem);
@@ -189,7 +196,7 @@ __global__ void __launch_bounds__(kThreads, TESSL_GEMV_MMA_MIN_BLOCKS) q4_gemv_m
     auto done = [&](uint32_t s) { return bars + 8 * (2 * S + s); };
     // M = 1: each warp stages its slice of x once (512 bytes of B fragments + the group sums) and the
     // lanes read their fragments back, instead of every lane converting the 64 values it holds.
-    const uint32_t xstage = ((bars + 24 * S + 15u) & ~15u) + (uint32_t)warp * kXStageBytes;
+    const uint32_t xstage = ((bars + 24 * S + 15u) & ~15u) + (uint32_t)warp * (kXStageBytes * NWIN);
 
     const uint32_t rb_lo = (uint32_t)((uint64_t)p.total_rb * blockIdx.x / gridDim.x);
     const uint32_t rb_hi = (uint32_t)((uint64_t)p.total_rb * (blockIdx.x + 1) / gridDim.x);
@@ -232,7 +239,7 @@ __global__ void __launch_bounds__(kThreads, TESSL_GEMV_MMA_MIN_BLOCKS) q4_gemv_m
         const uint32_t mg = (uint32_t)lane & 7u, mhi = ((uint32_t)lane >> 3) & 1u;
         const uint32_t my_bank = lane < 16 ? mg / HP : (sb_by_row ? 0u : (uint32_t)lane - 16);
         const uint32_t my_r = lane < 16 ? 2 * (mg % HP) + mhi : (sb_by_row ? (uint32_t)lane - 16 : 0u);
-        const bool copies = sb_by_row || lane < 16 + NB;
+        const bool copies = lane < 16 ? mg < HP * NB : (sb_by_row ? lane - 16 < RPB : lane < 16 + NB);
         const uint32_t my_dst = lane < 16 ? mg * pair_pitch + mhi * row_bytes
                                           : off_sb + (sb_by_row ? my_r : my_bank * RPB) * sb_row_bytes;
         uint32_t s = 0, ph = 0, issued = 0;
@@ -406,7 +413,8 @@ __global__ void __launch_bounds__(kThreads, TESSL_GEMV_MMA_MIN_BLOCKS) q4_gemv_m
     } else {
         // ------------------------------------------------ consumers ---
         const uint32_t g = lane >> 2, t = lane & 3;
-        const uint32_t k0 = (uint32_t)warp * (K / kConsumers);  // first column of this warp's slice
+        const uint32_t KW = K / NWIN;                             // columns of one window
+        const uint32_t k0 = (uint32_t)warp * (KW / kConsumers);  // first column of this warp's slice within a window
         const uint32_t G = 1u << p.group_shift;
         // x is written by the preceding kernel in a decode chain: wait for it.
         asm volatile("griddepcontrol.wait;" ::: "memory");
@@ -421,6 +429,20 @@ __global__ void __launch_bounds__(kThreads, TESSL_GEMV_MMA_MIN_BLOCKS) q4_gemv_m
         // product is a normal f32), the partners of the odd nibbles divided by 16 as well. Both are changes
         // of the exponent field only, hence exact; `cw` = 2^(133 - e) undoes them in the fold.
         float cw = 0.0f;
+        float cwv[NWIN];  // per window (M = 1)
+        // this lane's B fragments and group sums of window `win`, from the warp's staged copy
+        auto load_x = [&](int win) {
+            const uint32_t xst = xstage + win * kXStageBytes;
+#pragma unroll
+            for (int jj = 0; jj < NGS; ++jj) {
+#pragma unroll
+                for (int u = 0; u < WPG; ++u) {
+                    const uint4 f = q4k::lds128(xst + (jj * 4 * WPG + t * WPG + u) * 16);
+                    xb[jj * WPG + u][0] = f.x, xb[jj * WPG + u][1] = f.y, xb[jj * WPG + u][2] = f.z, xb[jj * WPG + u][3] = f.w;
+                }
+                xs[jj] = __uint_as_float(lds32(xst + 512 + jj * 4));
+            }
+        };
         {
             const uint32_t n = BATCH ? min(g, p.m - 1) : 0u;
             const uint16_t *xrow = p.x + (size_t)n * p.x_pitch;
@@ -452,38 +474,36 @@ __global__ void __launch_bounds__(kThreads, TESSL_GEMV_MMA_MIN_BLOCKS) q4_gemv_m
             auto pair = [&](uint32_t lo, uint32_t hi, int ee) { return scaled(lo & 0xffffu, ee) | (scaled(hi & 0xffffu, ee) << 16); };
             if constexpr (!BATCH && !Q8) {
                 constexpr uint32_t NW = 4 * SW;  // 8-column words of the slice: lane L < NW handles word L
-                uint4 r = make_uint4(0u, 0u, 0u, 0u);
-                if ((uint32_t)lane < NW) r = __ldg(reinterpret_cast<const uint4 *>(xrow + k0 + 8 * lane));
-                uint32_t amax = max(max(r.x & 0x7fffu, (r.x >> 16) & 0x7fffu), max(r.y & 0x7fffu, (r.y >> 16) & 0x7fffu));
-                amax = max(amax, max(max(r.z & 0x7fffu, (r.z >> 16) & 0x7fffu), max(r.w & 0x7fffu, (r.w >> 16) & 0x7fffu)));
 #pragma unroll
-                for (int o = 16; o > 0; o >>= 1) amax = max(amax, __shfl_xor_sync(0xffffffffu, amax, o));
-                if ((amax >> 7) != 0) {
-                    const int maxexp = (int)(amax >> 7) - 127;
-                    e = min(126, max(100, maxexp + 6)) - maxexp;
-                    cw = __uint_as_float((uint32_t)(127 + 133 - e) << 23);
-                }
-                if ((uint32_t)lane < NW) {
-                    asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(xstage + lane * 16), "r"(pair(r.x, r.z, e)),
-                                 "r"(pair(r.x >> 16, r.z >> 16, e - 4)), "r"(pair(r.y, r.w, e)), "r"(pair(r.y >> 16, r.w >> 16, e - 4))
-                                 : "memory");
-                }
-                float part = (dev::bf16_lo(r.x) + dev::bf16_hi(r.x)) + (dev::bf16_lo(r.y) + dev::bf16_hi(r.y));
-                part += (dev::bf16_lo(r.z) + dev::bf16_hi(r.z)) + (dev::bf16_lo(r.w) + dev::bf16_hi(r.w));
+                for (int win = 0; win < NWIN; ++win) {
+                    const uint32_t xst = xstage + win * kXStageBytes;
+                    uint4 r = make_uint4(0u, 0u, 0u, 0u);
+                    if ((uint32_t)lane < NW) r = __ldg(reinterpret_cast<const uint4 *>(xrow + win * KW + k0 + 8 * lane));
+                    uint32_t amax = max(max(r.x & 0x7fffu, (r.x >> 16) & 0x7fffu), max(r.y & 0x7fffu, (r.y >> 16) & 0x7fffu));
+                    amax = max(amax, max(max(r.z & 0x7fffu, (r.z >> 16) & 0x7fffu), max(r.w & 0x7fffu, (r.w >> 16) & 0x7fffu)));
 #pragma unroll
-                for (int o = 1; o < 4 * WPG && o < 32; o <<= 1) part += __shfl_xor_sync(0xffffffffu, part, o);  // a group: 4 WPG lanes
-                const float gsum = __shfl_sync(0xffffffffu, part, (lane * 4 * WPG) & 31);
-                if (lane < NGS) asm volatile("st.shared.f32 [%0], %1;" ::"r"(xstage + 512 + lane * 4), "f"(gsum) : "memory");
-                __syncwarp();
-#pragma unroll
-                for (int jj = 0; jj < NGS; ++jj) {
-#pragma unroll
-                    for (int u = 0; u < WPG; ++u) {
-                        const uint4 f = q4k::lds128(xstage + (jj * 4 * WPG + t * WPG + u) * 16);
-                        xb[jj * WPG + u][0] = f.x, xb[jj * WPG + u][1] = f.y, xb[jj * WPG + u][2] = f.z, xb[jj * WPG + u][3] = f.w;
+                    for (int o = 16; o > 0; o >>= 1) amax = max(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+                    e = 0, cw = 0.0f;
+                    if ((amax >> 7) != 0) {
+                        const int maxexp = (int)(amax >> 7) - 127;
+                        e = min(126, max(100, maxexp + 6)) - maxexp;
+                        cw = __uint_as_float((uint32_t)(127 + 133 - e) << 23);
                     }
-                    xs[jj] = __uint_as_float(lds32(xstage + 512 + jj * 4));
+                    cwv[win] = cw;
+                    if ((uint32_t)lane < NW) {
+                        asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(xst + lane * 16), "r"(pair(r.x, r.z, e)),
+                                     "r"(pair(r.x >> 16, r.z >> 16, e - 4)), "r"(pair(r.y, r.w, e)), "r"(pair(r.y >> 16, r.w >> 16, e - 4))
+                                     : "memory");
+                    }
+                    float part = (dev::bf16_lo(r.x) + dev::bf16_hi(r.x)) + (dev::bf16_lo(r.y) + dev::bf16_hi(r.y));
+                    part += (dev::bf16_lo(r.z) + dev::bf16_hi(r.z)) + (dev::bf16_lo(r.w) + dev::bf16_hi(r.w));
+#pragma unroll
+                    for (int o = 1; o < 4 * WPG && o < 32; o <<= 1) part += __shfl_xor_sync(0xffffffffu, part, o);  // a group: 4 WPG lanes
+                    const float gsum = __shfl_sync(0xffffffffu, part, (lane * 4 * WPG) & 31);
+                    if (lane < NGS) asm volatile("st.shared.f32 [%0], %1;" ::"r"(xst + 512 + lane * 4), "f"(gsum) : "memory");
                 }
+                __syncwarp();
+                if constexpr (NWIN == 1) load_x(0);
             } else
 #pragma unroll
             for (int jj = 0; jj < NGS; ++jj) {
@@ -543,13 +563,18 @@ __global__ void __launch_bounds__(kThreads, TESSL_GEMV_MMA_MIN_BLOCKS) q4_gemv_m
                 break;
             }
             const uint32_t st = ring + s * stage_bytes;
-            const uint32_t row_lo = st + g * pair_pitch + w_off, row_hi = row_lo + row_bytes;
-            const uint32_t sb_lo = st + off_sb + 2 * g * sb_row_bytes + sb_off, sb_hi = sb_lo + sb_row_bytes;
+            float vlo = 0.0f, vhi = 0.0f;  // M = 1: this lane's share of MMA rows g and g + 8, over all windows
+            float acc[4][4] = {};
+#pragma unroll
+            for (int win = 0; win < NWIN; ++win) {
+            if constexpr (NWIN > 1) load_x(win), cw = cwv[win];
+            const uint32_t row_lo = st + g * pair_pitch + w_off + win * (KW >> 1), row_hi = row_lo + row_bytes;
+            const uint32_t sb_lo = st + off_sb + 2 * g * sb_row_bytes + sb_off + win * ((KW >> p.group_shift) * 4);
+            const uint32_t sb_hi = sb_lo + sb_row_bytes;
             float dlo[NGS], dhi[NGS];        // M = 1: dot of MMA rows g and g + 8 per group
             // BATCH: rows g, g + 8 x columns 2 t, 2 t + 1, one accumulator per group class jj % 4 so that
             // the sum is formed in the same order as in the M = 1 path (where lane t of a quad takes
             // the groups t, t + 4, ... and the quad is then added up by a butterfly)
-            float acc[4][4] = {};
             // All words of the slice first (the rows were copied long ago: these loads do not wait),
             // then the MMAs interleaved over the groups: consecutive MMAs belong to different
             // accumulator chains, so none waits for its predecessor. Within a chain the order is
@@ -621,20 +646,8 @@ __global__ void __launch_bounds__(kThreads, TESSL_GEMV_MMA_MIN_BLOCKS) q4_gemv_m
                     dlo[jj] = d[jj][0], dhi[jj] = d[jj][2];  // every column holds the same vector: d[1] == d[0]
                 }
             }
-            const uint32_t part = st + off_part;
-            if constexpr (BATCH) {
-                float o[4];
-#pragma unroll
-                for (int c = 0; c < 4; ++c) o[c] = (acc[c][0] + acc[c][1]) + (acc[c][2] + acc[c][3]);
-                asm volatile("st.shared.v2.f32 [%0], {%1,%2};" ::"r"(part + ((warp * 16 + g) * 8 + 2 * t) * 4), "f"(o[0]),
-                             "f"(o[1])
-                             : "memory");
-                asm volatile("st.shared.v2.f32 [%0], {%1,%2};" ::"r"(part + ((warp * 16 + g + 8) * 8 + 2 * t) * 4),
-                             "f"(o[2]), "f"(o[3])
-                             : "memory");
-            } else {
+            if constexpr (!BATCH) {
                 // The four lanes of a quad hold the same dots: lane t folds the affine of groups t, t + 4, ...
-                float vlo = 0.0f, vhi = 0.0f;
 #pragma unroll
                 for (int q = 0; q < NQ; ++q) {
                     float dl = 0.0f, dh = 0.0f, xg = 0.0f;
@@ -648,6 +661,20 @@ __global__ void __launch_bounds__(kThreads, TESSL_GEMV_MMA_MIN_BLOCKS) q4_gemv_m
                         vhi = fmaf(dev::bf16_lo(ph2), dh * cw, fmaf(dev::bf16_hi(ph2), xg, vhi));
                     }
                 }
+            }
+            }  // windows
+            const uint32_t part = st + off_part;
+            if constexpr (BATCH) {
+                float o[4];
+#pragma unroll
+                for (int c = 0; c < 4; ++c) o[c] = (acc[c][0] + acc[c][1]) + (acc[c][2] + acc[c][3]);
+                asm volatile("st.shared.v2.f32 [%0], {%1,%2};" ::"r"(part + ((warp * 16 + g) * 8 + 2 * t) * 4), "f"(o[0]),
+                             "f"(o[1])
+                             : "memory");
+                asm volatile("st.shared.v2.f32 [%0], {%1,%2};" ::"r"(part + ((warp * 16 + g + 8) * 8 + 2 * t) * 4),
+                             "f"(o[2]), "f"(o[3])
+                             : "memory");
+            } else {
                 vlo += __shfl_xor_sync(0xffffffffu, vlo, 1), vhi += __shfl_xor_sync(0xffffffffu, vhi, 1);
                 vlo += __shfl_xor_sync(0xffffffffu, vlo, 2), vhi += __shfl_xor_sync(0xffffffffu, vhi, 2);
                 if (t == 0) {
