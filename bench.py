@@ -49,6 +49,7 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 HIDDEN, QKV, INTER, GROUP = 4096, 6144, 12288, 64
+TRAFFIC_RATIO = 1.0013  # ncu dram__bytes_read.sum + write.sum over algorithmic bytes, q4_gemv_mma_kernel at 12288 x 4096
 METRIC = "Q4 GEMV effective weight GB/s"
 
 
@@ -883,20 +884,22 @@ def main():
     }
     if world == 1:
         pk = ctx["per_kernel"]
-        # Dominant kernel: the bulk-copy staged GEMV (qkv, o and gate/up launches of a step).
-        dom = ["qkv 6144x4096", "o 4096x4096", "gate_up_silu 2x12288x4096"]
-        dom_bytes = q4_weight_bytes(QKV, HIDDEN) + q4_weight_bytes(HIDDEN, HIDDEN) + 2 * q4_weight_bytes(INTER, HIDDEN)
+        # Dominant kernel: the tensor-core GEMV, which serves all four launches of a step.
+        dom = ["qkv 6144x4096", "o 4096x4096", "gate_up_silu 2x12288x4096", "down 4096x12288"]
+        dom_bytes = STEP_WEIGHT_BYTES
         dom_us = sum(pk[k]["us"] for k in dom)
         achieved = dom_bytes / dom_us / 1e3
         line["roofline"] = {
             "bound": "hbm", "kernel": "q4_gemv_mma_kernel", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"],
             "unit": "GB/s", "frac": round(achieved / peaks["hbm_gbs"], 4), "peak_source": peaks["source"],
-            # ncu: dram__bytes_read+write of one 12288x4096 launch was 28.35 MB for 28.31 MB algorithmic
-            # (profiles/q4_gemv_mma_12288x4096.md): traffic = algorithmic bytes x 1.0013 per launch.
-            "traffic": round(dom_bytes / 3 * 1.0013), "algorithmic_bytes_per_launch": dom_bytes // 3,
-            "traffic_source": "one ncu capture of a 12288x4096 launch (28.35 MB DRAM for 28.31 MB algorithmic), scaled by "
-                              "bytes to the mean of this step's three launches of the kernel",
-            "launches_per_step": 3,
+            "how": "algorithmic weight bytes of the step's four launches / the sum of their average launch durations, each "
+                   "measured with CUDA events over a graph of that launch alone rotating over the layers' banks",
+            # ncu: dram__bytes_read+write of one 12288x4096 launch against its algorithmic bytes
+            # (profiles/q4_gemv_mma_12288x4096.md); scaled by bytes to the mean launch of the step.
+            "traffic": round(dom_bytes / 4 * TRAFFIC_RATIO), "algorithmic_bytes_per_launch": dom_bytes // 4,
+            "traffic_source": f"one ncu capture of a 12288x4096 launch (DRAM bytes / algorithmic bytes = {TRAFFIC_RATIO}), scaled "
+                              "by bytes to the mean of the step's four launches",
+            "launches_per_step": 4,
         }
         line["per_kernel"] = pk
         line["e2e"] = measure_e2e(ctx, args, local_rank)
