@@ -394,6 +394,10 @@ bool launch_mma_windows(TesslRuntime *rt, const Q4GemvParams &p, int m, int nb, 
 template <int SW, int WPG>
 Result launch_mma_q8_sw(TesslRuntime *rt, const Q4GemvParams &p, int m)
 {
+    // 4096 codes per row: a 16-row stage with the batch's partial sums is 77 KB and only two fit; 8-row stages
+    // (half of each MMA idle, which this format can afford: one MMA per 8 bytes of weights) give five.
+    if (SW == 16 && m > 1) return launch_mma_one<SW, WPG, 1, true, true, 1, 8>(rt, p, m);
+    if (m == 1) return launch_mma_one<SW, WPG, 1, false, true>(rt, p, m);
     return launch_mma_one<SW, WPG, 1, true, true>(rt, p, m);
 }
 
@@ -544,16 +548,15 @@ Result check_alignment(const TesslQ4MlxBank &b, const std::string &what)
 namespace nn {
 
 /// MLX Q8 (unsigned codes, bf16 pairs, bf16 x, M <= 8) on the tensor-core GEMV kernel: a row of `cols`
-/// codes runs as a row of 2 cols nibbles with groups of 2 group_size. `*handled` is false when the shape is
+/// codes is laid out and staged like a row of 2 cols nibbles with groups of 2 group_size (the kernel's sizes
+/// are in nibbles); the codes themselves go to the MMA as bf16 bit patterns, two per register. `*handled` is false when the shape is
 /// not one the kernel is built for (the caller then uses its FMA-pipe kernel).
 Result q8_mlx_mma(TesslRuntime *rt, const TesslBuf &codes, const TesslBuf &sb, const TesslBuf &x_bf16, const TesslBuf &y,
                   uint32_t rows, uint32_t cols, uint32_t group_size, uint32_t m, OutKind out, bool *handled)
 {
     *handled = false;
     if (!mma_enabled()) return ok();
-    // One vector stays on the FMA-pipe kernel (14336 x 4096: 19.0 us there, 19.9 us here); from two rows on
-    // this kernel costs the same as one (23 us at M = 4 and 8 against 35 and 55 us).
-    if (m < 2) return ok();
+    if (m < 1) return ok();
     if (cols != 512 && cols != 1024 && cols != 2048 && cols != 4096) return ok();
     if (group_size != 32 && group_size != 64) return ok();
     if (((uintptr_t)sb.ptr & 15u) != 0 || ((uintptr_t)x_bf16.ptr & 7u) != 0) return ok();

@@ -375,7 +375,7 @@ __global__ void __launch_bounds__(kThreads, TESSL_GEMV_MMA_MIN_BLOCKS) q4_gemv_m
                     v[2] += __uint_as_float(q.z), v[3] += __uint_as_float(q.w);
                 }
                 const uint32_t row = row0 + 2 * (r & 7u) + (r >> 3);  // MMA row r holds local row 2 (r % 8) + r / 8
-                if (row < sg.rows) {
+                if ((r & 7u) < (uint32_t)(ROWS / 2) && row < sg.rows) {
 #pragma unroll
                     for (int c = 0; c < 4; ++c) {
                         const uint32_t n = c0 + c;
@@ -447,15 +447,21 @@ __global__ void __launch_bounds__(kThreads, TESSL_GEMV_MMA_MIN_BLOCKS) q4_gemv_m
             const uint32_t n = BATCH ? min(g, p.m - 1) : 0u;
             const uint16_t *xrow = p.x + (size_t)n * p.x_pitch;
             int e = 0;
-            if constexpr (BATCH && !Q8) {
+            if constexpr (BATCH || Q8) {
                 uint32_t amax = 0;
 #pragma unroll
                 for (int jj = 0; jj < NGS; ++jj) {
 #pragma unroll
                     for (int u = 0; u < WPG; ++u) {
-                        const uint4 r = __ldg(reinterpret_cast<const uint4 *>(xrow + k0 + jj * G + t * (G / 4) + 8 * u));
-                        amax = max(amax, max(max(r.x & 0x7fffu, (r.x >> 16) & 0x7fffu), max(r.y & 0x7fffu, (r.y >> 16) & 0x7fffu)));
-                        amax = max(amax, max(max(r.z & 0x7fffu, (r.z >> 16) & 0x7fffu), max(r.w & 0x7fffu, (r.w >> 16) & 0x7fffu)));
+                        const uint32_t k = k0 + jj * G + t * (G / 4) + 8 * u;
+                        if constexpr (Q8) {
+                            const uint2 r = __ldg(reinterpret_cast<const uint2 *>(xrow + k / 2));
+                            amax = max(amax, max(max(r.x & 0x7fffu, (r.x >> 16) & 0x7fffu), max(r.y & 0x7fffu, (r.y >> 16) & 0x7fffu)));
+                        } else {
+                            const uint4 r = __ldg(reinterpret_cast<const uint4 *>(xrow + k));
+                            amax = max(amax, max(max(r.x & 0x7fffu, (r.x >> 16) & 0x7fffu), max(r.y & 0x7fffu, (r.y >> 16) & 0x7fffu)));
+                            amax = max(amax, max(max(r.z & 0x7fffu, (r.z >> 16) & 0x7fffu), max(r.w & 0x7fffu, (r.w >> 16) & 0x7fffu)));
+                        }
                     }
                 }
                 amax = max(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
@@ -512,18 +518,13 @@ __global__ void __launch_bounds__(kThreads, TESSL_GEMV_MMA_MIN_BLOCKS) q4_gemv_m
                 for (int u = 0; u < WPG; ++u) {
                     const uint32_t k = k0 + jj * G + t * (G / 4) + 8 * u;
                     if constexpr (Q8) {
-                        // the word's 8 nibbles are the low and high halves of 4 codes: nibble pairs (0,4), (1,5),
-                        // (2,6), (3,7) = low of codes 0,2 | high of codes 0,2 | low of 1,3 | high of 1,3
+                        // the word holds 4 codes; a code 0..255 read as a bf16 bit pattern is c * 2^-133 exactly (the
+                        // subnormals and the first binade form one linear scale), so (w & 0x00ff00ff) is an A register
+                        // of codes 0, 2 and ((w >> 8) & 0x00ff00ff) one of codes 1, 3: no magic constant, no offset
                         const uint2 r = __ldg(reinterpret_cast<const uint2 *>(xrow + k / 2));
-                        const float x0 = dev::bf16_lo(r.x), x1 = dev::bf16_hi(r.x), x2 = dev::bf16_lo(r.y), x3 = dev::bf16_hi(r.y);
-                        auto pack16 = [](float a, float b) {  // (16 a, 16 b) as bf16: exact, a power of two
-                            return (__float_as_uint(16.0f * a) >> 16) | (__float_as_uint(16.0f * b) & 0xffff0000u);
-                        };
-                        xb[jj * WPG + u][0] = __byte_perm(r.x, r.y, 0x5410);  // x0, x2
-                        xb[jj * WPG + u][1] = pack16(x0, x2);
-                        xb[jj * WPG + u][2] = __byte_perm(r.x, r.y, 0x7632);  // x1, x3
-                        xb[jj * WPG + u][3] = pack16(x1, x3);
-                        part += (x0 + x1) + (x2 + x3);
+                        xb[jj * WPG + u][0] = pair(r.x, r.y, e);              // x0, x2
+                        xb[jj * WPG + u][1] = pair(r.x >> 16, r.y >> 16, e);  // x1, x3
+                        part += (dev::bf16_lo(r.x) + dev::bf16_hi(r.x)) + (dev::bf16_lo(r.y) + dev::bf16_hi(r.y));
                     } else {
                         const uint4 r = __ldg(reinterpret_cast<const uint4 *>(xrow + k));
                         xb[jj * WPG + u][0] = pair(r.x, r.z, e);                  // x0, x4
@@ -551,8 +552,6 @@ __global__ void __launch_bounds__(kThreads, TESSL_GEMV_MMA_MIN_BLOCKS) q4_gemv_m
                 xs1[jj] = __shfl_sync(0xffffffffu, xs[jj], (2 * t + 1) * 4);
             }
         }
-        // what the 128 + q trick adds to a group's dot: 128 per nibble, i.e. 128 (x + 16 x) per code when Q8
-        constexpr float kOffset = Q8 ? -128.0f * 17.0f : -128.0f;
         const uint32_t w_off = (k0 >> 1) + t * (G / 8);  // byte offset of the lane's first word within a row
         const uint32_t sb_off = (k0 >> p.group_shift) * 4;
 
@@ -568,8 +567,10 @@ __global__ void __launch_bounds__(kThreads, TESSL_GEMV_MMA_MIN_BLOCKS) q4_gemv_m
 #pragma unroll
             for (int win = 0; win < NWIN; ++win) {
             if constexpr (NWIN > 1) load_x(win), cw = cwv[win];
-            const uint32_t row_lo = st + g * pair_pitch + w_off + win * (KW >> 1), row_hi = row_lo + row_bytes;
-            const uint32_t sb_lo = st + off_sb + 2 * g * sb_row_bytes + sb_off + win * ((KW >> p.group_shift) * 4);
+            // lane groups beyond the stage's row pairs (ROWS < 16) read the last pair again: their MMA rows are never stored
+            const uint32_t gp = min(g, (uint32_t)(ROWS / 2 - 1));
+            const uint32_t row_lo = st + gp * pair_pitch + w_off + win * (KW >> 1), row_hi = row_lo + row_bytes;
+            const uint32_t sb_lo = st + off_sb + 2 * gp * sb_row_bytes + sb_off + win * ((KW >> p.group_shift) * 4);
             const uint32_t sb_hi = sb_lo + sb_row_bytes;
             float dlo[NGS], dhi[NGS];        // M = 1: dot of MMA rows g and g + 8 per group
             // BATCH: rows g, g + 8 x columns 2 t, 2 t + 1, one accumulator per group class jj % 4 so that
@@ -600,10 +601,8 @@ __global__ void __launch_bounds__(kThreads, TESSL_GEMV_MMA_MIN_BLOCKS) q4_gemv_m
                 for (int jj = 0; jj < NGS; ++jj) {
                     const uint32_t a = wl[jj * WPG + u], b = wh[jj * WPG + u];
                     if constexpr (Q8) {
-                        // nibble pairs (i, i + 4) as two bf16 values 128 + q: exactly an A-fragment register
-                        const uint32_t a0 = and_or(a, 0x000f000fu, kMagic), b0 = and_or(b, 0x000f000fu, kMagic);
-                        const uint32_t a1 = and_or(a >> 4, 0x000f000fu, kMagic), b1 = and_or(b >> 4, 0x000f000fu, kMagic);
-                        mma_bf16(d[jj], a0, b0, a1, b1, xb[jj * WPG + u][0], xb[jj * WPG + u][1]);  // columns 0,4 | 1,5
+                        mma_bf16(d[jj], a & 0x00ff00ffu, b & 0x00ff00ffu, (a >> 8) & 0x00ff00ffu, (b >> 8) & 0x00ff00ffu,
+                                 xb[jj * WPG + u][0], xb[jj * WPG + u][1]);  // codes 0,2 | 1,3
                     } else {
                         // nibble pairs (0, 4) and 16 x (1, 5) in place: five ALU instructions per word instead of
                         // seven (these share the busiest pipe of the kernel), and nothing to subtract afterwards
@@ -614,11 +613,7 @@ __global__ void __launch_bounds__(kThreads, TESSL_GEMV_MMA_MIN_BLOCKS) q4_gemv_m
 #pragma unroll
                 for (int jj = 0; jj < NGS; ++jj) {
                     const uint32_t a = wl[jj * WPG + u], b = wh[jj * WPG + u];
-                    if constexpr (Q8) {
-                        const uint32_t a2 = and_or(a >> 8, 0x000f000fu, kMagic), b2 = and_or(b >> 8, 0x000f000fu, kMagic);
-                        const uint32_t a3 = and_or(a >> 12, 0x000f000fu, kMagic), b3 = and_or(b >> 12, 0x000f000fu, kMagic);
-                        mma_bf16(d[jj], a2, b2, a3, b3, xb[jj * WPG + u][2], xb[jj * WPG + u][3]);  // columns 2,6 | 3,7
-                    } else {
+                    if constexpr (!Q8) {
                         const uint32_t as = a >> 8, bs = b >> 8;
                         mma_bf16(d[jj], as & 0x000f000fu, bs & 0x000f000fu, as & 0x00f000f0u, bs & 0x00f000f0u, xb[jj * WPG + u][2],
                                  xb[jj * WPG + u][3]);
@@ -631,17 +626,10 @@ __global__ void __launch_bounds__(kThreads, TESSL_GEMV_MMA_MIN_BLOCKS) q4_gemv_m
                     const uint32_t pl = lds32(sb_lo + jj * 4), ph2 = lds32(sb_hi + jj * 4);
                     const float sl = dev::bf16_lo(pl), bl = dev::bf16_hi(pl), sh = dev::bf16_lo(ph2), bh = dev::bf16_hi(ph2);
                     const int cls = jj & 3;  // a constant once the loop is unrolled
-                    if constexpr (Q8) {
-                        acc[0][cls] = fmaf(sl, fmaf(kOffset, xs0[jj], d[jj][0]), fmaf(bl, xs0[jj], acc[0][cls]));
-                        acc[1][cls] = fmaf(sl, fmaf(kOffset, xs1[jj], d[jj][1]), fmaf(bl, xs1[jj], acc[1][cls]));
-                        acc[2][cls] = fmaf(sh, fmaf(kOffset, xs0[jj], d[jj][2]), fmaf(bh, xs0[jj], acc[2][cls]));
-                        acc[3][cls] = fmaf(sh, fmaf(kOffset, xs1[jj], d[jj][3]), fmaf(bh, xs1[jj], acc[3][cls]));
-                    } else {
-                        acc[0][cls] = fmaf(sl, d[jj][0] * cw0, fmaf(bl, xs0[jj], acc[0][cls]));
-                        acc[1][cls] = fmaf(sl, d[jj][1] * cw1, fmaf(bl, xs1[jj], acc[1][cls]));
-                        acc[2][cls] = fmaf(sh, d[jj][2] * cw0, fmaf(bh, xs0[jj], acc[2][cls]));
-                        acc[3][cls] = fmaf(sh, d[jj][3] * cw1, fmaf(bh, xs1[jj], acc[3][cls]));
-                    }
+                    acc[0][cls] = fmaf(sl, d[jj][0] * cw0, fmaf(bl, xs0[jj], acc[0][cls]));
+                    acc[1][cls] = fmaf(sl, d[jj][1] * cw1, fmaf(bl, xs1[jj], acc[1][cls]));
+                    acc[2][cls] = fmaf(sh, d[jj][2] * cw0, fmaf(bh, xs0[jj], acc[2][cls]));
+                    acc[3][cls] = fmaf(sh, d[jj][3] * cw1, fmaf(bh, xs1[jj], acc[3][cls]));
                 } else {
                     dlo[jj] = d[jj][0], dhi[jj] = d[jj][2];  // every column holds the same vector: d[1] == d[0]
                 }
