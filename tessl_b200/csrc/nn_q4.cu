@@ -1,11 +1,11 @@
-// MLX affine Q4 GEMV (M = 1) and small-batch GEMM (M <= 8) for sm_100a, with the
-// host-side wrappers that mirror the reference's `nn::gemv_q4_mlx_*` and
-// `nn::gemm_q4_mlx` (src/nn.rs:3982-4619 of the reference project).
+// MLX affine Q4 GEMV (M = 1) and small-batch GEMM (M <= 8) for sm_100a: the host-side wrappers that mirror
+// the reference's `nn::gemv_q4_mlx_*`, `nn::gemm_q4_mlx` and `nn::embed_lookup_q4_mlx` (src/nn.rs:3592-4619 of
+// the reference project): validation in the reference's order and wording, the choice of kernel and
+// instantiation, the launch.
 //
-// The kernel itself (and the reasoning behind its shape) is in
-// q4_gemv_kernel.cuh / q4_gemv_main.cuh; this file holds the host wrappers:
-// validation in the reference's order and wording, the choice of instantiation,
-// the launch.
+// Kernels: q4_gemv_mma.cuh (the default: dot products on the tensor cores, bulk-copy ring; also the MLX Q8 mode
+// and the column-sharded launches that exchange their outputs over NVLink), and the FMA-pipe fallbacks
+// q4_gemv_tma.cuh, q4_gemv_warp.cuh, q4_gemv_main.cuh / q4_gemv_kernel.cuh for the shapes it does not take.
 #include "q4_gemv_main.cuh"
 #include "q4_gemv_warp.cuh"
 #include "q4_gemv_tma.cuh"
