@@ -244,7 +244,7 @@ TESSL_API int32_t tessl_gemm_q4_mlx_tensorops_bf16(TesslRuntime *rt, TesslQ4MlxB
  * (K_aug = 64 * (ceil(K/64) + ceil(4*(K/G)/64)); e.g. up to m = 963 at K = 4096,
  * G = 64). Arguments, validation, kernels and results are those of
  * tessl_gemm_q4_mlx_tensorops. The first call on a device looks the array's
- * address up; make that call before capturing a stream. All calls on a device
+ * address up (a synchronous query of the CUDA runtime). All calls on a device
  * share the array: it keeps the previous call's contents (every byte a call
  * reads is rewritten by that call first, so nothing needs clearing), and calls
  * that overlap on the GPU race on it - serialise them. */

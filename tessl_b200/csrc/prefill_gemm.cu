@@ -637,7 +637,7 @@ Result gemm_q4_mlx_tensorops(TesslRuntime *rt, const TesslQ4MlxBank &bank, const
 /// that do not fit. Same validation, same kernels, same bits.
 ///
 /// The first call on a device resolves the array's address (no allocation, but
-/// a runtime call: make it before any stream capture). The array is shared by
+/// a synchronous query of the CUDA runtime). The array is shared by
 /// every call and every runtime on that device and keeps the last call's
 /// contents; the pre-pass rewrites every byte a call later reads, so nothing has
 /// to start at zero, but two calls that overlap on the GPU (two streams, two

@@ -1,9 +1,10 @@
 """`tessl_peer_gather`: the NVLink peer-memory all-gather behind the column-sharded
 GEMVs (no counterpart in the reference, a single-device library).
 
-On one GPU only the argument checks and the world == 1 no-op can run; with two or
-more GPUs two ranks (child processes, NCCL only for the rendezvous, NVLS off) gather
-changing patterns several times and compare every byte.
+On one GPU only the argument checks, the world == 1 no-op and a wait that runs out can
+run; with two or more GPUs two ranks (child processes, NCCL only for the rendezvous, NVLS
+off) gather changing patterns several times - a one-block slice, then 512 KiB slices
+copied by sixteen blocks, eagerly and replayed from a CUDA graph - and compare every byte.
 """
 import ctypes
 import os
@@ -102,6 +103,36 @@ for call in range(5):
         want = (np.arange(n, dtype=np.int32) + 1000 * r + 7 * call).astype(np.int16)
         assert np.array_equal(got[r], want), (rank, call, r)
     dist.barrier()   # nobody starts overwriting its slice before everyone has checked
+# slices large enough for several thread blocks (the ticket counter, the last block's completion
+# handshake, the counters' reset), eagerly and replayed from a CUDA graph
+big = 512 * 1024 // 2  # bf16 elements per rank: 512 KiB, 16 blocks
+pgb = sharded.PeerGather(big * 2)
+def fill(call):
+    pgb.local(torch.int16).copy_(torch.arange(big, device="cuda", dtype=torch.int32).mul_(3).add_(1000 * rank + 7 * call).to(torch.int16))
+def check(call, what):
+    got = pgb.full(torch.int16).cpu().numpy().reshape(world, big)
+    for r in range(world):
+        want = (np.arange(big, dtype=np.int64) * 3 + 1000 * r + 7 * call).astype(np.int16)
+        assert np.array_equal(got[r], want), (rank, what, call, r)
+for call in range(4):
+    with torch.cuda.stream(st):
+        fill(call)
+    pgb.run(rt)
+    check(call, "eager")
+    dist.barrier()
+rt.set_encode_only(True)
+graph = torch.cuda.CUDAGraph()
+with torch.cuda.graph(graph, stream=st):
+    for i in range(3):
+        pgb.run(rt)
+for rep in range(3):
+    with torch.cuda.stream(st):
+        fill(100 + rep)
+        graph.replay()
+    rt.synchronize()
+    check(100 + rep, "graph")
+    dist.barrier()
+rt.set_encode_only(False)
 assert not rt.is_poisoned()
 dist.destroy_process_group()
 print("peer gather ok", rank)
