@@ -102,6 +102,7 @@ struct Params {
     uint32_t row_pitch;
     uint32_t sb_pitch;
     uint32_t x_pitch;
+    uint32_t quads;  // fetch four rows per bulk copy (long streams, one bank, one row of x)
     uint32_t *status;
     Peer peer;
 };
@@ -185,6 +186,15 @@ __global__ void __launch_bounds__(kThreads, TESSL_GEMV_MMA_MIN_BLOCKS) q4_gemv_m
     // copy more than per byte, and sixteen 2 KB copies per stage bounded the stream. Pairs sit 32 bytes
     // past a multiple of 128 apart (bank-conflict-free fragment reads).
     const uint32_t pair_pitch = 2 * row_bytes + kRowPad;
+    // Long streams (`quads`): two pairs back to back so that one copy fetches four rows - eight copies of 4 KB
+    // per stage still cost the copy unit more than the bytes do, four of 8 KB reach the pure read rate - with
+    // the quads 32 bytes past a multiple of 128 apart. The two pairs of a quad then share banks (a two-way
+    // conflict on every fragment read), which costs short launches more than the copies save: the host sets
+    // it from the launch's stages per SM. Pure data movement: results do not depend on it.
+    const bool quads = NB == 1 && !BATCH && p.quads != 0;
+    auto pair_off = [&](uint32_t gi) {
+        return quads ? (gi >> 1) * (4 * row_bytes + kRowPad) + (gi & 1u) * 2 * row_bytes : gi * pair_pitch;
+    };
     const uint32_t part_bytes = BATCH ? kConsumers * 16 * 8 * 4 : kConsumers * 16 * 4;
     const uint32_t off_sb = (ROWS / 2) * 2 * pitch, off_part = off_sb + ROWS * sb_row_bytes;
     const uint32_t stage_bytes = off_part + part_bytes;
@@ -240,7 +250,7 @@ __global__ void __launch_bounds__(kThreads, TESSL_GEMV_MMA_MIN_BLOCKS) q4_gemv_m
         const uint32_t my_bank = lane < 16 ? mg / HP : (sb_by_row ? 0u : (uint32_t)lane - 16);
         const uint32_t my_r = lane < 16 ? 2 * (mg % HP) + mhi : (sb_by_row ? (uint32_t)lane - 16 : 0u);
         const bool copies = lane < 16 ? mg < HP * NB : (sb_by_row ? lane - 16 < RPB : lane < 16 + NB);
-        const uint32_t my_dst = lane < 16 ? mg * pair_pitch + mhi * row_bytes
+        const uint32_t my_dst = lane < 16 ? pair_off(mg) + mhi * row_bytes
                                           : off_sb + (sb_by_row ? my_r : my_bank * RPB) * sb_row_bytes;
         uint32_t s = 0, ph = 0, issued = 0;
         int cur_seg = -1;
@@ -284,7 +294,9 @@ __global__ void __launch_bounds__(kThreads, TESSL_GEMV_MMA_MIN_BLOCKS) q4_gemv_m
                         bulk_g2s(st + my_dst, src, sb_row_bytes, full(s));
                     }
                 } else if (pair_copy) {
-                    if (mhi == 0 && my_r < nrows) bulk_g2s(st + my_dst, src, my_r + 1 < nrows ? 2 * row_bytes : row_bytes, full(s));
+                    if (quads && nrows == RPB) {
+                        if (mhi == 0 && (mg & 1u) == 0 && mg < HP) bulk_g2s(st + my_dst, src, (mg + 1 < HP ? 4 : 2) * row_bytes, full(s));
+                    } else if (mhi == 0 && my_r < nrows) bulk_g2s(st + my_dst, src, my_r + 1 < nrows ? 2 * row_bytes : row_bytes, full(s));
                 } else if (my_r < nrows) {
                     bulk_g2s(st + my_dst, src, row_bytes, full(s));
                 }
@@ -569,7 +581,7 @@ __global__ void __launch_bounds__(kThreads, TESSL_GEMV_MMA_MIN_BLOCKS) q4_gemv_m
             if constexpr (NWIN > 1) load_x(win), cw = cwv[win];
             // lane groups beyond the stage's row pairs (ROWS < 16) read the last pair again: their MMA rows are never stored
             const uint32_t gp = min(g, (uint32_t)(ROWS / 2 - 1));
-            const uint32_t row_lo = st + gp * pair_pitch + w_off + win * (KW >> 1), row_hi = row_lo + row_bytes;
+            const uint32_t row_lo = st + pair_off(gp) + w_off + win * (KW >> 1), row_hi = row_lo + row_bytes;
             const uint32_t sb_lo = st + off_sb + 2 * gp * sb_row_bytes + sb_off + win * ((KW >> p.group_shift) * 4);
             const uint32_t sb_hi = sb_lo + sb_row_bytes;
             float dlo[NGS], dhi[NGS];        // M = 1: dot of MMA rows g and g + 8 per group

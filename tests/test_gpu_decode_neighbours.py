@@ -9,7 +9,7 @@ the reference project.
 import numpy as np
 import pytest
 
-from gpu_util import SENTINEL_F32, rt, seeded_f32, upload_bank  # noqa: F401
+from gpu_util import SENTINEL_F32, assert_north_star, rt, seeded_f32, upload_bank  # noqa: F401
 from oracle import api
 from tessl_b200 import nn, synth
 
@@ -151,3 +151,59 @@ def test_norm_refusals(rt):
     nn.qwen35_rms_norm(rt, xb, wb, out, False, 0, dim, 1e-6)
     nn.qwen35_add_rms_norm(rt, yb, xb, wb, out, True, 0, dim, 1e-6)
     assert rt.take_dispatch_count() == 0
+
+
+def test_an_mlp_block_is_three_launches_and_replays_from_a_graph(rt):
+    """The steps either side of the projections in decode (src/qwen35_model.rs:1630-1687, 1938-1957 of the
+    reference project): resid += y_prev; x = bf16(rms_norm(resid)); mid = bf16(silu(W_gate x) * (W_up x));
+    resid += W_down mid. Three launches; every stage checked against the oracle with the same rounding points;
+    then the same three calls captured once and replayed."""
+    import torch
+
+    hidden, inter, group, eps = 4096, 12288, 64, 1e-6
+    gp, gs = synth.q4_bank(0x7E550A00, inter, hidden, group)
+    up, us = synth.q4_bank(0x7E550A10, inter, hidden, group)
+    dp, ds = synth.q4_bank(0x7E550A20, hidden, inter, group)
+    gate, upb, down = upload_bank(rt, gp, gs), upload_bank(rt, up, us), upload_bank(rt, dp, ds)
+    resid0, y_prev, w = _norm_inputs(1, hidden, 0x7E550A30)
+    wb, yb = rt.buffer_from(w), rt.buffer_from(y_prev)
+    resid = rt.buffer_from(resid0)
+    xb = rt.alloc_buffer(hidden * 2)
+    mid = rt.alloc_buffer(inter * 2)
+
+    def block():
+        nn.qwen35_add_rms_norm(rt, yb, resid, wb, xb, True, 1, hidden, eps)
+        nn.gemv_q4_mlx_gate_up_silu(rt, gate, upb, xb, mid, nn.QuantShape(inter, hidden, group), True)
+        nn.gemv_q4_mlx_simd(rt, down, mid, resid, nn.QuantShape(hidden, inter, group), resid=resid)
+
+    rt.take_dispatch_count()
+    block()
+    assert rt.take_dispatch_count() == 3
+    # oracle, stage by stage, fed with the device's own rounded intermediates so that each stage is checked alone
+    r1 = (resid0 + y_prev).astype(np.float32)
+    x_dev = xb.read(np.uint16, hidden)
+    want_x = api.qwen35_rms_norm_f64(resid0, w, 1, hidden, eps, resid_add=y_prev)[0]
+    np.testing.assert_allclose(synth.bf16_bits_to_f32(x_dev), want_x, rtol=8e-3, atol=1e-6)
+    g = api.q4_dense_gemm(gp.view(np.uint8).reshape(-1), gs.reshape(-1), x_dev, 1, inter, hidden, group)[0].astype(np.float64)
+    u = api.q4_dense_gemm(up.view(np.uint8).reshape(-1), us.reshape(-1), x_dev, 1, inter, hidden, group)[0].astype(np.float64)
+    mid_dev = mid.read(np.uint16, inter)
+    assert_north_star(synth.bf16_bits_to_f32(mid_dev), (g / (1.0 + np.exp(-g)) * u).astype(np.float32), "mid")
+    d = api.q4_dense_gemm(dp.view(np.uint8).reshape(-1), ds.reshape(-1), mid_dev, 1, hidden, inter, group)[0]
+    got = resid.read(np.float32, hidden)
+    assert_north_star(got - r1, d, "down")
+    # captured once, replayed twice on a fresh residual: the same bits as the eager run
+    st = torch.cuda.ExternalStream(rt.stream)
+    resid.write(resid0)
+    rt.set_encode_only(True)
+    try:
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=st):
+            block()
+        for _ in range(2):
+            resid.write(resid0)
+            with torch.cuda.stream(st):
+                graph.replay()
+            rt.synchronize()
+            assert np.array_equal(resid.read(np.uint32, hidden), got.view(np.uint32))
+    finally:
+        rt.set_encode_only(False)

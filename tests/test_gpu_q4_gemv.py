@@ -18,7 +18,9 @@ pytestmark = pytest.mark.gpu
 
 REF_SHAPES = [(r, k, g) for _, r, k, g in rc.SHAPES]
 MODEL_SHAPES = [(4096, 4096, 64), (6144, 4096, 64), (4096, 12288, 64), (1000, 2048, 128), (257, 4096, 32),
-                (12288, 4096, 64), (96, 1024, 512), (64, 512, 256)]
+                (12288, 4096, 64), (96, 1024, 512), (64, 512, 256),
+                # eight or more stages per SM: the producer fetches four rows per copy; ragged last block
+                (19001, 4096, 64), (19030, 1024, 128)]
 
 
 def make_case(rows, cols, group, seed):
