@@ -554,7 +554,9 @@ def measure_sharded_lm_head(ctx, args, world, rank):
         yl_b = B(y_local)
         slot = per
     shape = nn.QuantShape(sh.local_rows, cols, GROUP)
-    iters = 2 * nslices
+    # many calls per replay: the ranks leave the barrier before a replay tens of microseconds apart, and the
+    # first call of a replay waits for the last rank to arrive
+    iters = 16 * nslices
 
     def call(i):
         if peer is not None:

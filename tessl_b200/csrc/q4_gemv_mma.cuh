@@ -343,7 +343,10 @@ __global__ void __launch_bounds__(kThreads, TESSL_GEMV_MMA_MIN_BLOCKS) q4_gemv_m
             const uint32_t part = ring + s * stage_bytes + off_part;
             if constexpr (!BATCH) {
                 // lane r < RPB: output row row0 + r (for a gate/up pair also its up partner, MMA row r + 8)
-                if (lane < RPB && row0 + lane < sg.rows) {
+                const bool live = lane < RPB && row0 + lane < sg.rows;
+                const uint32_t row = row0 + lane;
+                float v = 0.0f;
+                if (live) {
                     float v0 = 0.0f, v1 = 0.0f;
                     // local row l sits in MMA row (l odd ? 8 : 0) + l / 2; its up partner RPB / 2 rows further
                     const uint32_t mrow = (((uint32_t)lane & 1u) << 3) + ((uint32_t)lane >> 1);
@@ -352,8 +355,7 @@ __global__ void __launch_bounds__(kThreads, TESSL_GEMV_MMA_MIN_BLOCKS) q4_gemv_m
                         v0 += __uint_as_float(lds32(part + (w * 16 + mrow) * 4));
                         if (NB == 2) v1 += __uint_as_float(lds32(part + (w * 16 + mrow + RPB / 2) * 4));
                     }
-                    const uint32_t row = row0 + lane;
-                    float v = v0;
+                    v = v0;
                     if (p.epi == q4k::EPI_ADD_RESID) {
                         v = v + sg.resid[row];
                     } else if (p.epi == q4k::EPI_GATE_UP_SILU) {
@@ -361,18 +363,66 @@ __global__ void __launch_bounds__(kThreads, TESSL_GEMV_MMA_MIN_BLOCKS) q4_gemv_m
                     } else if (p.epi == q4k::EPI_GATE_UP_GELU) {
                         v = dev::gelu_pytorch_tanh(v0) * v1;
                     }
+                }
+                // The partial sums are in registers: the stage may be refilled while the outputs are stored (stores to
+                // a peer GPU take their time, and the producer waits for this arrival).
+                __syncwarp();
+                if (lane == 0) mbar_arrive(empty(s));
+                const uint32_t hbits = p.out_bf16 ? (uint32_t)dev::f32_to_bf16_store(v) : __float_as_uint(v);
+                if (live) {
                     if (p.out_bf16) {
-                        const uint16_t h = dev::f32_to_bf16_store(v);
-                        static_cast<uint16_t *>(sg.out)[row] = h;
-                        if (peered) {
-                            for (uint32_t r = 0; r < p.peer.world; ++r)
-                                if (r != p.peer.rank) reinterpret_cast<uint16_t *>(p.peer.out[r])[row] = h;
-                        }
+                        static_cast<uint16_t *>(sg.out)[row] = (uint16_t)hbits;
                     } else {
                         static_cast<float *>(sg.out)[row] = v;
-                        if (peered) {
-                            for (uint32_t r = 0; r < p.peer.world; ++r)
-                                if (r != p.peer.rank) reinterpret_cast<float *>(p.peer.out[r])[row] = v;
+                    }
+                }
+                if (peered) {
+                    if (row0 + RPB <= sg.rows) {
+                        // A whole block: every lane collects the block's outputs, and lane L stores them to peer L with
+                        // 16-byte stores - one or a few store instructions per stage for all peers together, where a
+                        // store per row and peer made the reducer the slowest part of a sharded launch.
+                        const bool to_peer = (uint32_t)lane < p.peer.world && (uint32_t)lane != p.peer.rank;
+                        if (p.out_bf16) {
+                            const uint32_t word = (hbits & 0xffffu) | (__shfl_down_sync(0xffffffffu, hbits, 1) << 16);
+                            uint32_t wv[RPB / 2];
+#pragma unroll
+                            for (int i = 0; i < RPB / 2; ++i) wv[i] = __shfl_sync(0xffffffffu, word, 2 * i);
+                            if (to_peer) {
+                                uint8_t *dst = p.peer.out[lane] + (size_t)row0 * 2;
+                                if constexpr (RPB % 8 == 0) {  // blocks start on 16-byte boundaries
+#pragma unroll
+                                    for (int i = 0; i < RPB / 8; ++i)
+                                        reinterpret_cast<uint4 *>(dst)[i] = make_uint4(wv[4 * i], wv[4 * i + 1], wv[4 * i + 2], wv[4 * i + 3]);
+                                } else {  // 14-row blocks start on 4-byte boundaries
+#pragma unroll
+                                    for (int i = 0; i < RPB / 2; ++i) reinterpret_cast<uint32_t *>(dst)[i] = wv[i];
+                                }
+                            }
+                        } else {
+                            uint32_t fv[RPB];
+#pragma unroll
+                            for (int i = 0; i < RPB; ++i) fv[i] = __shfl_sync(0xffffffffu, hbits, i);
+                            if (to_peer) {
+                                uint32_t *dst = reinterpret_cast<uint32_t *>(p.peer.out[lane] + (size_t)row0 * 4);
+                                if constexpr (RPB % 4 == 0) {
+#pragma unroll
+                                    for (int i = 0; i < RPB / 4; ++i)
+                                        reinterpret_cast<uint4 *>(dst)[i] = make_uint4(fv[4 * i], fv[4 * i + 1], fv[4 * i + 2], fv[4 * i + 3]);
+                                } else {
+#pragma unroll
+                                    for (int i = 0; i < RPB / 2; ++i) reinterpret_cast<uint2 *>(dst)[i] = make_uint2(fv[2 * i], fv[2 * i + 1]);
+                                }
+                            }
+                        }
+                    } else if (live) {
+                        // the bank's ragged last block: one store per row and peer
+                        for (uint32_t r = 0; r < p.peer.world; ++r) {
+                            if (r == p.peer.rank) continue;
+                            if (p.out_bf16) {
+                                reinterpret_cast<uint16_t *>(p.peer.out[r])[row] = (uint16_t)hbits;
+                            } else {
+                                reinterpret_cast<float *>(p.peer.out[r])[row] = v;
+                            }
                         }
                     }
                 }
@@ -404,8 +454,10 @@ __global__ void __launch_bounds__(kThreads, TESSL_GEMV_MMA_MIN_BLOCKS) q4_gemv_m
                     }
                 }
             }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(empty(s));  // partial sums read: the stage may be refilled
+            if constexpr (BATCH) {
+                __syncwarp();
+                if (lane == 0) mbar_arrive(empty(s));  // partial sums read: the stage may be refilled
+            }
             if (++s == S) s = 0, ph ^= 1u;
         }
         if (peered && good) {

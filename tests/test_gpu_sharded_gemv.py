@@ -140,7 +140,9 @@ def xs(seed, cols):
 
 # (rows, cols, group, bf16 out): the tensor-core kernel with several stages per block, a ragged slice,
 # and a width that kernel does not take (the GEMV + stand-alone exchange path)
-for rows, cols, group, bf16 in ((12288, 4096, 64, True), (4104, 2048, 32, False), (1000, 1536, 64, False)):
+# and rows of 8192 / 12288 columns (windowed stages; 14-row blocks whose slots are only 4-byte aligned in bf16)
+for rows, cols, group, bf16 in ((12288, 4096, 64, True), (4104, 2048, 32, False), (1000, 1536, 64, False),
+                                (1000, 12288, 64, True), (4096, 12288, 64, False), (520, 8192, 128, True)):
     elem, tdt = (2, torch.int16) if bf16 else (4, torch.int32)
     gp, gsb = dev_bank(100 + rows, rows, cols, group)
     up, usb = dev_bank(200 + rows, rows, cols, group)
