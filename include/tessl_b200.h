@@ -67,6 +67,9 @@ typedef struct TesslQ4MlxBank {
  * Apple-GPU repack no Qwen3.5 path uses) is refused by name. */
 #define TESSL_Q4_ROW_MAJOR 0u
 #define TESSL_Q4_INTERLEAVED4 1u
+/* An offline repack for this library's GEMV kernel (the role Interleaved4 plays on
+ * Apple GPUs; no counterpart in the reference): see tessl_q4_mlx_repack_staged. */
+#define TESSL_Q4_B200_STAGED 2u
 
 /* src/nn.rs:4408-4415. */
 typedef struct TesslQkvOutputs {
@@ -402,6 +405,32 @@ TESSL_API int32_t tessl_mlx_q4_read_bank(const TesslCheckpoint *ck, const char *
 TESSL_API int32_t tessl_mlx_q4_load_bank(TesslRuntime *rt, const TesslCheckpoint *ck, const char *const *weight_names,
                                const uint64_t *rows, uint32_t nparts, uint64_t cols, TesslQ4MlxBank bank, char *err,
                                size_t err_len);
+
+/* ----------------------------------------------------- offline repack --- */
+
+/* The B200 staged layout of one MLX Q4 bank [rows, cols], cols in {1024, 2048,
+ * 4096}, group_size in {32, 64, 128}: NO COUNTERPART IN THE REFERENCE (its own
+ * repack, Interleaved4, serves Apple GPUs: kernels/q4_mlx_dot.h:28-31). The bank
+ * becomes ceil(rows / 8) units of 8 rows, each unit the exact bytes the GEMV kernel
+ * keeps in shared memory: four pairs of adjacent packed rows (row 2i, row 2i + 1,
+ * then 32 zero bytes), then the eight rows' (scale, bias) pairs; rows past the end
+ * are zeros. A stage of the kernel is then two bulk copies instead of nine or
+ * ten. The nibbles and pairs themselves are unchanged, and so is every result:
+ * an entry given a staged bank returns the bits it returns for the row-major bank.
+ * tessl_q4_mlx_staged_bytes gives the size (0 for a shape outside the domain);
+ * tessl_q4_mlx_repack_staged writes the staged image of `bank` into `out`.
+ * A staged bank is passed as TesslQ4MlxBank{packed = the image, scales_biases =
+ * {NULL, 0}} with layout TESSL_Q4_B200_STAGED to tessl_gemv_q4_mlx_simd[_bf16],
+ * tessl_gemv_q4_mlx_gate_up_gelu and tessl_gemv_q4_mlx_gate_up_silu_layout; the
+ * other entries refuse it by name. */
+TESSL_API uint64_t tessl_q4_mlx_staged_bytes(uint32_t rows, uint32_t cols, uint32_t group_size);
+TESSL_API int32_t tessl_q4_mlx_repack_staged(TesslRuntime *rt, TesslQ4MlxBank bank, TesslQuantShape shape, TesslBuf out,
+                                   char *err, size_t err_len);
+/* tessl_gemv_q4_mlx_gate_up_silu with a layout argument (the reference's SiLU
+ * entry is row-major only, src/nn.rs:4165-4194). */
+TESSL_API int32_t tessl_gemv_q4_mlx_gate_up_silu_layout(TesslRuntime *rt, TesslQ4MlxBank gate, TesslQ4MlxBank up,
+                                              TesslBuf x_bf16, TesslBuf mid, TesslQuantShape shape, uint32_t layout,
+                                              uint32_t mid_as_bf16, char *err, size_t err_len);
 
 /* ------------------------------------------------------- parity helpers --- */
 

@@ -265,3 +265,24 @@ def qwen35_rms_norm_f64(x, w, rows, dim, eps, resid_add=None) -> np.ndarray:
     inv = 1.0 / np.sqrt((v64 * v64).mean(axis=1, keepdims=True) + np.float64(np.float32(eps)))
     wp = (np.float32(1.0) + np.asarray(w, np.float32).reshape(dim)).astype(np.float64)
     return v64 * inv * wp
+
+
+def q4_repack_b200_staged(packed, sb, rows, cols, group) -> np.ndarray:
+    """The B200 staged image of a bank, as bytes: units of 8 rows, each four pairs of adjacent packed rows (row 2i,
+    row 2i + 1, 32 zero bytes) followed by the eight rows' (scale, bias) pairs; rows past the end are zeros. The
+    library's own repack (no counterpart in the reference, whose Interleaved4 plays this role on Apple GPUs,
+    tests/q4_interleaved.rs:54-83 of the reference project, holds its repack oracle the same way)."""
+    row_bytes, sb_row = cols // 2, (cols // group) * 4
+    pair_pitch = 2 * row_bytes + 32
+    unit = 4 * pair_pitch + 8 * sb_row
+    units = (rows + 7) // 8
+    p = np.zeros((units * 8, row_bytes), np.uint8)
+    p[:rows] = np.ascontiguousarray(packed).view(np.uint8).reshape(rows, row_bytes)
+    s = np.zeros((units * 8, sb_row), np.uint8)
+    s[:rows] = np.ascontiguousarray(sb).view(np.uint8).reshape(rows, sb_row)
+    out = np.zeros((units, unit), np.uint8)
+    pairs = p.reshape(units, 4, 2 * row_bytes)
+    for i in range(4):
+        out[:, i * pair_pitch: i * pair_pitch + 2 * row_bytes] = pairs[:, i]
+    out[:, 4 * pair_pitch:] = s.reshape(units, 8 * sb_row)
+    return out.reshape(-1)

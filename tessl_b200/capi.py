@@ -13,7 +13,7 @@ from pathlib import Path
 
 ABI_VERSION = 1
 TESSL_OK, TESSL_ERR, TESSL_PANIC = 0, 1, 2
-ROW_MAJOR, INTERLEAVED4 = 0, 1
+ROW_MAJOR, INTERLEAVED4, B200_STAGED = 0, 1, 2
 GEMM_Q4_MLX_MAX_M = 8
 
 LIB_PATH = Path(__file__).resolve().parent / "_lib" / "libtessl_b200.so"
@@ -115,6 +115,9 @@ SIGNATURES = {
                                            C.c_void_p, C.c_uint64, C.c_void_p, C.c_uint64] + _ERR),
     "tessl_mlx_q4_load_bank": (C.c_int32, [_RT, C.c_void_p, C.POINTER(C.c_char_p), C.POINTER(C.c_uint64), _u32, C.c_uint64,
                                            Q4MlxBank] + _ERR),
+    "tessl_q4_mlx_staged_bytes": (C.c_uint64, [_u32, _u32, _u32]),
+    "tessl_q4_mlx_repack_staged": (C.c_int32, [_RT, Q4MlxBank, QuantShape, Buf] + _ERR),
+    "tessl_gemv_q4_mlx_gate_up_silu_layout": (C.c_int32, [_RT, Q4MlxBank, Q4MlxBank, Buf, Buf, QuantShape, _u32, _u32] + _ERR),
     "tessl_q4_mlx_unpack": (C.c_int32, [_RT, Q4MlxBank, QuantShape, Buf] + _ERR),
     "tessl_q4_mlx_dequant": (C.c_int32, [_RT, Q4MlxBank, QuantShape, Buf] + _ERR),
 }

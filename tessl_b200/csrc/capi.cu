@@ -479,6 +479,27 @@ int32_t tessl_gemv_q4_mlx_gate_up_silu_sharded(TesslRuntime *rt, TesslQ4MlxBank 
     });
 }
 
+uint64_t tessl_q4_mlx_staged_bytes(uint32_t rows, uint32_t cols, uint32_t group_size)
+{
+    return tessl::nn::q4_mlx_staged_bytes(rows, cols, group_size);
+}
+
+int32_t tessl_q4_mlx_repack_staged(TesslRuntime *rt, TesslQ4MlxBank bank, TesslQuantShape shape, TesslBuf out, char *err,
+                                   size_t err_len)
+{
+    return guarded(rt, err, err_len, true, [&] { return tessl::nn::q4_mlx_repack_staged(rt, bank, shape, out); });
+}
+
+int32_t tessl_gemv_q4_mlx_gate_up_silu_layout(TesslRuntime *rt, TesslQ4MlxBank gate, TesslQ4MlxBank up, TesslBuf x_bf16,
+                                              TesslBuf mid, TesslQuantShape shape, uint32_t layout, uint32_t mid_as_bf16,
+                                              char *err, size_t err_len)
+{
+    return guarded(rt, err, err_len, true, [&] {
+        return tessl::nn::gemv_q4_mlx_gate_up(rt, "gemv_q4_mlx_simd_gate_up_silu", "gemv_q4_mlx_gate_up_silu", true, gate,
+                                              up, x_bf16, mid, shape, layout, mid_as_bf16 != 0);
+    });
+}
+
 int32_t tessl_q4_weight_matmul(TesslRuntime *rt, TesslQ4MlxBank bank, uint32_t rows, uint32_t cols, TesslBuf x_bf16,
                                uint32_t m, TesslBuf y, const TesslBuf *resid, char *err, size_t err_len)
 {

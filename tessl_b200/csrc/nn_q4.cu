@@ -46,6 +46,44 @@ __global__ void q4_unpack_kernel(const uint8_t *packed, uint8_t *out, uint64_t n
     out[2 * i + 1] = b >> 4;
 }
 
+/// Geometry of the staged layout for rows of `cols` columns and groups of `group` (see q4_gemv_mma.cuh).
+struct StagedGeom {
+    uint32_t row_bytes, pair_pitch, sb_row_bytes, unit_bytes;
+};
+__host__ __device__ inline StagedGeom staged_geom(uint32_t cols, uint32_t group)
+{
+    StagedGeom g;
+    g.row_bytes = cols / 2;
+    g.pair_pitch = 2 * g.row_bytes + q4m::kRowPad;
+    g.sb_row_bytes = (cols / group) * 4;
+    g.unit_bytes = 4 * g.pair_pitch + 8 * g.sb_row_bytes;
+    return g;
+}
+
+/// One thread per 16 bytes of the staged image: a piece of a packed row, of a pad, or of a scale/bias row.
+__global__ void q4_repack_staged_kernel(const uint4 *packed, const uint4 *sb, uint4 *out, uint32_t rows, uint32_t cols,
+                                        uint32_t group, uint64_t n16)
+{
+    const uint64_t i = (uint64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n16) return;
+    const StagedGeom g = staged_geom(cols, group);
+    const uint64_t byte = i * 16;
+    const uint32_t unit = (uint32_t)(byte / g.unit_bytes), o = (uint32_t)(byte % g.unit_bytes);
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (o < 4 * g.pair_pitch) {
+        const uint32_t pair = o / g.pair_pitch, within = o % g.pair_pitch;
+        if (within < 2 * g.row_bytes) {
+            const uint32_t row = 8 * unit + 2 * pair + within / g.row_bytes;
+            if (row < rows) v = packed[((size_t)row * g.row_bytes + within % g.row_bytes) / 16];
+        }
+    } else {
+        const uint32_t so = o - 4 * g.pair_pitch;
+        const uint32_t row = 8 * unit + so / g.sb_row_bytes;
+        if (row < rows) v = sb[((size_t)row * g.sb_row_bytes + so % g.sb_row_bytes) / 16];
+    }
+    out[i] = v;
+}
+
 __global__ void q4_dequant_kernel(const uint8_t *packed, const uint32_t *sb, float *out, uint32_t rows, uint32_t cols,
                                   uint32_t group_shift)
 {
@@ -240,7 +278,7 @@ bool mma_ok(const Q4GemvParams &p)
     if (p.cols != 1024 && p.cols != 2048 && p.cols != 4096) return false;
     if (p.group_shift < 5 || p.group_shift > 7) return false;
     if (((p.cols / 16) >> p.group_shift) == 0) return false;
-    for (int s = 0; s < p.nseg; ++s) {
+    for (int s = 0; s < p.nseg && !p.staged; ++s) {
         const Q4Seg &a = p.seg[s];
         if (((uintptr_t)a.sb0 & 15u) || (a.sb1 && ((uintptr_t)a.sb1 & 15u))) return false;
     }
@@ -278,6 +316,8 @@ Result launch_mma_one(TesslRuntime *rt, const Q4GemvParams &p, int m, const MmaW
     mp.sb_pitch = w.sb_pitch ? w.sb_pitch : (p.cols >> p.group_shift) * 4;
     mp.x_pitch = w.x_pitch ? w.x_pitch : (Q8 ? p.cols >> 1 : p.cols);
     mp.status = rt->status_dev;
+    mp.staged = p.staged ? 1u : 0u;
+    if (p.staged && (NWIN != 1 || ROWS != 16 || BATCH || Q8)) return "q4_gemv: the staged layout runs on the one-row Q4 kernel only";
     if (p.peer) {
         const TesslPeerGather &g = *static_cast<const TesslPeerGather *>(p.peer);
         if (BATCH || Q8 || p.nseg != 1) return "q4_gemv: a sharded launch has one bank (or one gate/up pair) and one row of x";
@@ -300,7 +340,7 @@ Result launch_mma_one(TesslRuntime *rt, const Q4GemvParams &p, int m, const MmaW
     const uint32_t grid = std::min<uint32_t>(rb, (uint32_t)rt->sm_count);
     // four-row copies from eight stages per SM on (18992 x 4096: 10.3 -> 9.8 us, 151936 x 4096: 58.8 -> 52.7 us;
     // 12288 x 4096, five to six stages: 7.66 -> 7.83 us)
-    mp.quads = (NB == 1 && !BATCH && NWIN == 1 && w.row_pitch == 0 && rb >= 8u * grid) ? 1u : 0u;
+    mp.quads = (NB == 1 && !BATCH && NWIN == 1 && w.row_pitch == 0 && !p.staged && rb >= 8u * grid) ? 1u : 0u;
     cudaLaunchConfig_t lc{};
     lc.gridDim = dim3(grid), lc.blockDim = dim3(q4m::kThreads), lc.dynamicSmemBytes = smem;
     lc.stream = rt->stream;
@@ -430,6 +470,8 @@ Result launch_q4_gemv(TesslRuntime *rt, Q4GemvParams p, int m, int nb)
         return nn::peer_gather(rt, *g);
     }
     const uint32_t nchunks = std::max<uint32_t>(1u, (p.cols + q4k::kChunk - 1) / q4k::kChunk);
+    if (p.staged && !(m == 1 && mma_ok(p)))
+        return "q4_gemv: the staged layout needs the tensor-core GEMV kernel (one row of x, rows of 1024, 2048 or 4096 columns)";
     if (m >= 1 && m <= 8 && (nb == 1 || m == 1) && mma_ok(p)) return launch_mma(rt, p, m, nb);
     if (mma_long_ok(p, m)) {
         // The kernel takes one bank per launch at these widths. The bank-routed forms run as one launch per
@@ -538,6 +580,28 @@ Q4Seg make_seg(const TesslQ4MlxBank &b0, const TesslQ4MlxBank *b1, const TesslBu
     return s;
 }
 
+bool staged_domain(uint32_t cols, uint32_t group)
+{
+    if (cols != 1024 && cols != 2048 && cols != 4096) return false;
+    if (group != 32 && group != 64 && group != 128) return false;
+    return (cols / 16) / group >= 1;
+}
+
+Result check_alignment(const TesslQ4MlxBank &b, const std::string &what);
+
+/// The bank checks of an entry that takes either layout: the reference's for a row-major bank, size,
+/// domain and alignment of the image for a staged one.
+Result bank_validate_layout(const TesslQ4MlxBank &bank, const TesslQuantShape &shape, uint32_t layout, const std::string &what)
+{
+    if (layout != TESSL_Q4_B200_STAGED) return q4_bank_validate(bank, shape, what);
+    TESSL_TRY(quant_shape_validate(shape, what));
+    if (!staged_domain(shape.cols, shape.group_size))
+        return fmt("%s: the B200 staged layout exists for rows of 1024, 2048 or 4096 columns and groups of 32, 64 or 128 "
+                   "(got %u columns, group %u)", what.c_str(), shape.cols, shape.group_size);
+    TESSL_TRY(require(bank.packed, nn::q4_mlx_staged_bytes(shape.rows, shape.cols, shape.group_size), 1, what + " staged image"));
+    return require_aligned16(bank.packed, what + " staged image");
+}
+
 Result check_alignment(const TesslQ4MlxBank &b, const std::string &what)
 {
     TESSL_TRY(require_aligned16(b.packed, what + " packed"));
@@ -592,8 +656,9 @@ Result gemv_q4_mlx_simd(TesslRuntime *rt, const TesslQ4MlxBank &bank, const Tess
                         const TesslQuantShape &shape, uint32_t layout, const TesslBuf *resid, OutKind out)
 {
     const char *entry = resid ? "gemv_q4_mlx_simd_add" : "gemv_q4_mlx_simd";
-    TESSL_TRY(refuse_layout(layout, entry));
-    TESSL_TRY(q4_bank_validate(bank, shape, entry));
+    const bool staged = layout == TESSL_Q4_B200_STAGED;
+    TESSL_TRY(refuse_layout(layout, entry, true));
+    TESSL_TRY(bank_validate_layout(bank, shape, layout, entry));
     TESSL_TRY(require(x_bf16, shape.cols, 2, std::string(entry) + " x_bf16"));
     TESSL_TRY(require(y, shape.rows, out == OUT_BF16 ? 2 : 4, std::string(entry) + " y"));
     if (resid) TESSL_TRY(require(*resid, shape.rows, 4, std::string(entry) + " resid"));
@@ -601,7 +666,7 @@ Result gemv_q4_mlx_simd(TesslRuntime *rt, const TesslQ4MlxBank &bank, const Tess
     const Named writes[] = {{"y", &y}};
     const Named reads[] = {{"packed", &bank.packed}, {"scales_biases", &bank.scales_biases}, {"x_bf16", &x_bf16}};
     TESSL_TRY(require_disjoint_writes(entry, writes, 1, reads, 3));
-    TESSL_TRY(check_alignment(bank, entry));
+    if (!staged) TESSL_TRY(check_alignment(bank, entry));
     TESSL_TRY(require_aligned16(x_bf16, std::string(entry) + " x_bf16"));
     if (shape.cols == 0) {
         // No columns: every sum is empty. The kernel's loop never runs and the
@@ -615,6 +680,7 @@ Result gemv_q4_mlx_simd(TesslRuntime *rt, const TesslQ4MlxBank &bank, const Tess
     p.group_shift = log2_u32(shape.group_size);
     p.epi = resid ? EPI_ADD_RESID : EPI_STORE;
     p.out_bf16 = out == OUT_BF16;
+    p.staged = staged;
     return launch_q4_gemv(rt, p, 1, 1);
 }
 
@@ -622,9 +688,10 @@ Result gemv_q4_mlx_gate_up(TesslRuntime *rt, const char *entry, const char *what
                            const TesslQ4MlxBank &gate, const TesslQ4MlxBank &up, const TesslBuf &x,
                            const TesslBuf &mid, const TesslQuantShape &shape, uint32_t layout, bool mid_as_bf16)
 {
-    TESSL_TRY(refuse_layout(layout, entry));
-    TESSL_TRY(q4_bank_validate(gate, shape, std::string(entry) + " gate"));
-    TESSL_TRY(q4_bank_validate(up, shape, std::string(entry) + " up"));
+    const bool staged = layout == TESSL_Q4_B200_STAGED;
+    TESSL_TRY(refuse_layout(layout, entry, true));
+    TESSL_TRY(bank_validate_layout(gate, shape, layout, std::string(entry) + " gate"));
+    TESSL_TRY(bank_validate_layout(up, shape, layout, std::string(entry) + " up"));
     TESSL_TRY(require(x, shape.cols, 2, std::string(entry) + " x"));
     if (mid_as_bf16) {
         TESSL_TRY(require(mid, shape.rows, 2, std::string(entry) + " mid (bf16)"));
@@ -639,10 +706,13 @@ Result gemv_q4_mlx_gate_up(TesslRuntime *rt, const char *entry, const char *what
                            {"up_scales_biases", &up.scales_biases},
                            {"x", &x}};
     TESSL_TRY(require_disjoint_writes(what, writes, 1, reads, 5));
-    TESSL_TRY(check_alignment(gate, std::string(entry) + " gate"));
-    TESSL_TRY(check_alignment(up, std::string(entry) + " up"));
+    if (!staged) {
+        TESSL_TRY(check_alignment(gate, std::string(entry) + " gate"));
+        TESSL_TRY(check_alignment(up, std::string(entry) + " up"));
+    }
     TESSL_TRY(require_aligned16(x, std::string(entry) + " x"));
     Q4GemvParams p{};
+    p.staged = staged;
     p.seg[0] = make_seg(gate, &up, mid, nullptr, shape.rows);
     p.nseg = 1;
     p.x = static_cast<const uint16_t *>(x.ptr);
@@ -909,6 +979,36 @@ Result embed_lookup_q4_mlx(TesslRuntime *rt, const TesslQ4MlxBank &bank, const T
         total32);
     rt->dispatch_count += 1;
     return cuda_check(rt, cudaGetLastError(), "embed_lookup_q4_mlx launch");
+}
+
+uint64_t q4_mlx_staged_bytes(uint32_t rows, uint32_t cols, uint32_t group_size)
+{
+    if (!staged_domain(cols, group_size)) return 0;
+    return (uint64_t)((rows + 7) / 8) * staged_geom(cols, group_size).unit_bytes;
+}
+
+Result q4_mlx_repack_staged(TesslRuntime *rt, const TesslQ4MlxBank &bank, const TesslQuantShape &shape, const TesslBuf &out)
+{
+    const char *entry = "q4_mlx_repack_staged";
+    TESSL_TRY(q4_bank_validate(bank, shape, entry));
+    if (!staged_domain(shape.cols, shape.group_size))
+        return fmt("%s: the B200 staged layout exists for rows of 1024, 2048 or 4096 columns and groups of 32, 64 or 128 "
+                   "(got %u columns, group %u)", entry, shape.cols, shape.group_size);
+    const uint64_t nbytes = q4_mlx_staged_bytes(shape.rows, shape.cols, shape.group_size);
+    TESSL_TRY(require(out, nbytes, 1, std::string(entry) + " out"));
+    if (shape.rows == 0) return ok();
+    const Named writes[] = {{"out", &out}};
+    const Named reads[] = {{"packed", &bank.packed}, {"scales_biases", &bank.scales_biases}};
+    TESSL_TRY(require_disjoint_writes(entry, writes, 1, reads, 2));
+    TESSL_TRY(require_aligned16(bank.packed, std::string(entry) + " packed"));
+    TESSL_TRY(require_aligned16(bank.scales_biases, std::string(entry) + " scales_biases"));
+    TESSL_TRY(require_aligned16(out, std::string(entry) + " out"));
+    const uint64_t n16 = nbytes / 16;
+    q4_repack_staged_kernel<<<(unsigned)((n16 + 255) / 256), 256, 0, rt->stream>>>(
+        static_cast<const uint4 *>(bank.packed.ptr), static_cast<const uint4 *>(bank.scales_biases.ptr),
+        static_cast<uint4 *>(out.ptr), shape.rows, shape.cols, shape.group_size, n16);
+    rt->dispatch_count += 1;
+    return cuda_check(rt, cudaGetLastError(), "q4_mlx_repack_staged launch");
 }
 
 Result q4_mlx_unpack(TesslRuntime *rt, const TesslQ4MlxBank &bank, const TesslQuantShape &shape, const TesslBuf &out)

@@ -64,6 +64,9 @@ struct Params {
     // Host side only: the TesslPeerGather of a column-sharded launch whose kernel exchanges its own
     // outputs (q4_gemv_mma.cuh), else null. Kernels other than that one never read it.
     const void *peer;
+    // Host side only: the banks are in the staged layout (units of 8 rows in the tensor-core kernel's
+    // shared-memory form); only that kernel takes them.
+    int staged;
 };
 
 constexpr int kChunk = 1024;  // columns one warp covers per step: 32 lanes x 32 nibbles

@@ -103,6 +103,10 @@ struct Params {
     uint32_t sb_pitch;
     uint32_t x_pitch;
     uint32_t quads;  // fetch four rows per bulk copy (long streams, one bank, one row of x)
+    // The banks are in the staged layout (tessl_q4_mlx_repack_staged): units of 8 rows already in this kernel's
+    // shared-memory form - four row pairs with their pads, then the rows' scale/bias pairs - so a stage is two
+    // bulk copies.
+    uint32_t staged;
     uint32_t *status;
     Peer peer;
 };
@@ -192,12 +196,20 @@ __global__ void __launch_bounds__(kThreads, TESSL_GEMV_MMA_MIN_BLOCKS) q4_gemv_m
     // conflict on every fragment read), which costs short launches more than the copies save: the host sets
     // it from the launch's stages per SM. Pure data movement: results do not depend on it.
     const bool quads = NB == 1 && !BATCH && p.quads != 0;
+    const bool staged = NWIN == 1 && ROWS == 16 && p.staged != 0;
+    const uint32_t unit_bytes = 4 * pair_pitch + 8 * sb_row_bytes;  // one staged unit: 8 rows
     auto pair_off = [&](uint32_t gi) {
+        if (staged) return (gi >> 2) * unit_bytes + (gi & 3u) * pair_pitch;
         return quads ? (gi >> 1) * (4 * row_bytes + kRowPad) + (gi & 1u) * 2 * row_bytes : gi * pair_pitch;
     };
     const uint32_t part_bytes = BATCH ? kConsumers * 16 * 8 * 4 : kConsumers * 16 * 4;
     const uint32_t off_sb = (ROWS / 2) * 2 * pitch, off_part = off_sb + ROWS * sb_row_bytes;
     const uint32_t stage_bytes = off_part + part_bytes;
+    // scale/bias rows of lane group gi's pair (local rows 2 gi and 2 gi + 1)
+    auto sb_pair_off = [&](uint32_t gi) {
+        if (staged) return (gi >> 2) * unit_bytes + 4 * pair_pitch + 2 * (gi & 3u) * sb_row_bytes;
+        return off_sb + 2 * gi * sb_row_bytes;
+    };
     const uint32_t S = p.stages;
     const uint32_t ring = smem_u32(smem);
     const uint32_t bars = ring + S * stage_bytes;
@@ -284,6 +296,21 @@ __global__ void __launch_bounds__(kThreads, TESSL_GEMV_MMA_MIN_BLOCKS) q4_gemv_m
             }
             const uint32_t nrows = min((uint32_t)RPB, seg_rows - row0);
             const uint32_t st = ring + s * stage_bytes;
+            if (staged) {
+                // one bank: units 2 b and 2 b + 1 of the block; a gate/up pair: unit b of each bank
+                const Seg &sg = p.seg[cur_seg];
+                const uint32_t ua = row0 / 8, ub = NB == 1 ? ua + 1 : ua;
+                const bool has_b = NB == 2 || ub < (seg_rows + 7) / 8;
+                if (lane == 0) mbar_expect_tx(full(s), (has_b ? 2u : 1u) * unit_bytes);
+                __syncwarp();
+                if (lane == 0) bulk_g2s(st, sg.packed0 + (size_t)ua * unit_bytes, unit_bytes, full(s));
+                if (lane == 1 && has_b)
+                    bulk_g2s(st + unit_bytes, (NB == 1 ? sg.packed0 : sg.packed1) + (size_t)ub * unit_bytes, unit_bytes, full(s));
+                row0 += RPB;
+                ++issued;
+                if (++s == S) s = 0, ph ^= 1u;
+                continue;
+            }
             if (lane == 0) mbar_expect_tx(full(s), NB * nrows * (row_bytes + sb_row_bytes));
             __syncwarp();
             if (copies) {
@@ -634,7 +661,7 @@ __global__ void __launch_bounds__(kThreads, TESSL_GEMV_MMA_MIN_BLOCKS) q4_gemv_m
             // lane groups beyond the stage's row pairs (ROWS < 16) read the last pair again: their MMA rows are never stored
             const uint32_t gp = min(g, (uint32_t)(ROWS / 2 - 1));
             const uint32_t row_lo = st + pair_off(gp) + w_off + win * (KW >> 1), row_hi = row_lo + row_bytes;
-            const uint32_t sb_lo = st + off_sb + 2 * gp * sb_row_bytes + sb_off + win * ((KW >> p.group_shift) * 4);
+            const uint32_t sb_lo = st + sb_pair_off(gp) + sb_off + win * ((KW >> p.group_shift) * 4);
             const uint32_t sb_hi = sb_lo + sb_row_bytes;
             float dlo[NGS], dhi[NGS];        // M = 1: dot of MMA rows g and g + 8 per group
             // BATCH: rows g, g + 8 x columns 2 t, 2 t + 1, one accumulator per group class jj % 4 so that

@@ -200,9 +200,14 @@ inline Result require_aligned16(const TesslBuf &b, const std::string &what)
     return ok();
 }
 
-inline Result refuse_layout(uint32_t layout, const char *entry)
+inline Result refuse_layout(uint32_t layout, const char *entry, bool takes_staged = false)
 {
     if (layout == TESSL_Q4_ROW_MAJOR) return ok();
+    if (layout == TESSL_Q4_B200_STAGED) {
+        if (takes_staged) return ok();
+        return fmt("%s: the B200 staged layout is taken by the one-row GEMV and gate/up entries only; pass a row-major bank",
+                   entry);
+    }
     if (layout == TESSL_Q4_INTERLEAVED4)
         return fmt("%s: the Interleaved4 layout is an Apple-GPU repack that this library does not build; "
                    "pass row-major banks", entry);
@@ -287,6 +292,8 @@ Result qwen35_add_rms_norm(TesslRuntime *rt, const TesslBuf &y, const TesslBuf &
                            bool out_as_bf16, uint32_t rows, uint32_t dim, float eps);
 Result embed_lookup_q4_mlx(TesslRuntime *rt, const TesslQ4MlxBank &bank, const TesslBuf &token_ids, const TesslBuf &out,
                            uint32_t vocab, uint32_t hidden, uint32_t group_size, uint32_t n_tokens);
+uint64_t q4_mlx_staged_bytes(uint32_t rows, uint32_t cols, uint32_t group_size);
+Result q4_mlx_repack_staged(TesslRuntime *rt, const TesslQ4MlxBank &bank, const TesslQuantShape &shape, const TesslBuf &out);
 Result q4_mlx_unpack(TesslRuntime *rt, const TesslQ4MlxBank &bank, const TesslQuantShape &shape, const TesslBuf &out);
 Result q4_mlx_dequant(TesslRuntime *rt, const TesslQ4MlxBank &bank, const TesslQuantShape &shape,
                       const TesslBuf &out);

@@ -19,6 +19,7 @@ from . import capi
 from .capi import Buf, Q4MlxBank as _CBank, QkvOutputs as _CQkv, QuantShape as _CShape, TesslError  # noqa: F401
 
 ROW_MAJOR = capi.ROW_MAJOR
+B200_STAGED = capi.B200_STAGED
 INTERLEAVED4 = capi.INTERLEAVED4
 GEMM_Q4_MLX_MAX_M = capi.GEMM_Q4_MLX_MAX_M
 GEMM_Q4_MLX_TENSOROPS_GROUP_SIZES = (32, 64, 128)
@@ -220,10 +221,31 @@ def gemv_q4_mlx_simd(rt: Runtime, bank: Q4MlxBank, x_bf16: GpuBuffer, y: GpuBuff
 
 
 def gemv_q4_mlx_gate_up_silu(rt: Runtime, gate: Q4MlxBank, up: Q4MlxBank, x: GpuBuffer, mid: GpuBuffer,
-                             shape: QuantShape, mid_as_bf16: bool) -> None:
-    """`nn::gemv_q4_mlx_gate_up_silu` (src/nn.rs:4165-4194)."""
-    capi.call("tessl_gemv_q4_mlx_gate_up_silu", rt.handle, gate.c(), up.c(), x.c(), mid.c(), shape.c(),
-              int(mid_as_bf16))
+                             shape: QuantShape, mid_as_bf16: bool, layout: int = ROW_MAJOR) -> None:
+    """`nn::gemv_q4_mlx_gate_up_silu` (src/nn.rs:4165-4194); `layout` other than row-major goes through the
+    library's own entry with a layout argument."""
+    if layout == ROW_MAJOR:
+        capi.call("tessl_gemv_q4_mlx_gate_up_silu", rt.handle, gate.c(), up.c(), x.c(), mid.c(), shape.c(),
+                  int(mid_as_bf16))
+    else:
+        capi.call("tessl_gemv_q4_mlx_gate_up_silu_layout", rt.handle, gate.c(), up.c(), x.c(), mid.c(), shape.c(), layout,
+                  int(mid_as_bf16))
+
+
+def q4_mlx_staged_bytes(rows: int, cols: int, group_size: int) -> int:
+    """Size of the B200 staged image of a bank; 0 for a shape the layout does not exist for."""
+    return int(capi.load().tessl_q4_mlx_staged_bytes(rows, cols, group_size))
+
+
+def q4_mlx_repack_staged(rt: Runtime, bank: Q4MlxBank, shape: QuantShape) -> Q4MlxBank:
+    """The bank repacked offline into the B200 staged layout (`tessl_q4_mlx_repack_staged`): pass the result with
+    `layout=B200_STAGED` to the one-row GEMV and gate/up operators. Results are those of the row-major bank."""
+    nbytes = q4_mlx_staged_bytes(shape.rows, shape.cols, shape.group_size)
+    if nbytes == 0 and shape.rows:
+        raise ValueError("the B200 staged layout exists for rows of 1024, 2048 or 4096 columns and groups of 32, 64 or 128")
+    out = rt.alloc_buffer(nbytes)
+    capi.call("tessl_q4_mlx_repack_staged", rt.handle, bank.c(), shape.c(), out.c())
+    return Q4MlxBank(out, GpuBuffer(0, 0))
 
 
 def gemv_q4_mlx_gate_up_gelu(rt: Runtime, gate: Q4MlxBank, up: Q4MlxBank, x: GpuBuffer, mid: GpuBuffer,
