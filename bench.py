@@ -338,8 +338,20 @@ def run_ours(args, rank: int, world: int, local_rank: int):
     sd_local = nn.QuantShape(layers[0].sh_down.local_rows, INTER, GROUP)
     launches_per_step = 4  # N > 1 with peer memory: still four, the exchange is inside the gate/up kernel
 
-    def step(i: int, down_sharded: bool = False):
+    # The offline repack (B200 staged layout) of the three launches it serves, for the variant timed beside the
+    # headline (one GPU): q/k/v, o and gate/up repacked, down (rows of 12288 columns) row-major.
+    # Built after the headline has been timed, so that nothing about the headline depends on it.
+    staged_banks = None
+
+    def step(i: int, down_sharded: bool = False, staged: bool = False):
         L = layers[i % n_layers]
+        if staged:
+            S = staged_banks[i % n_layers]
+            nn.gemv_q4_mlx_simd(rt, S["qkv"], bufs["x_qkv"], qkv_b, sq, layout=nn.B200_STAGED)
+            nn.gemv_q4_mlx_simd(rt, S["o"], bufs["x_o"], o_b, so, layout=nn.B200_STAGED)
+            nn.gemv_q4_mlx_gate_up_silu(rt, S["gate"], S["up"], bufs["x_mlp"], midl_b, sg, True, layout=nn.B200_STAGED)
+            nn.gemv_q4_mlx_simd(rt, L.down, midf_b, y_b, sd)
+            return y
         nn.gemv_q4_mlx_simd(rt, L.qkv, bufs["x_qkv"], qkv_b, sq)
         nn.gemv_q4_mlx_simd(rt, L.o, bufs["x_o"], o_b, so)
         if peer is not None:
@@ -370,13 +382,13 @@ def run_ours(args, rank: int, world: int, local_rank: int):
             step(i, True)
     barrier()
 
-    def timed_graph(down_sharded: bool, sample_clocks: bool):
+    def timed_graph(down_sharded: bool, sample_clocks: bool, staged: bool = False):
         # Launch-bound inner loop: one CUDA graph holds all K steps (kernels and, on the NCCL
         # fallback, the all-gathers, captured on the runtime's stream).
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph, stream=st):
             for i in range(args.steps):
-                step(i, down_sharded)
+                step(i, down_sharded, staged)
         with torch.cuda.stream(st):
             graph.replay()
         barrier()
@@ -414,8 +426,32 @@ def run_ours(args, rank: int, world: int, local_rank: int):
         variants = {"down replicated (the timed step)": round(ms_per_step * 1e3, 3),
                     "down row-sharded + exchange of its f32 outputs": round(ms_sharded_down * 1e3, 3), "unit": "us per step"}
 
+    staged_variant = None
+    if world == 1:
+        rt.set_encode_only(False)
+        sgu = nn.QuantShape(INTER, HIDDEN, GROUP)
+        staged_banks = [{"qkv": nn.q4_mlx_repack_staged(rt, L.qkv, sq), "o": nn.q4_mlx_repack_staged(rt, L.o, so),
+                         "gate": nn.q4_mlx_repack_staged(rt, L.gate, sgu), "up": nn.q4_mlx_repack_staged(rt, L.up, sgu)}
+                        for L in layers]
+        rt.set_encode_only(True)
+        for i in range(max(args.warmup, 3)):
+            step(i, False, True)
+        barrier()
+        ms_staged, _ = timed_graph(False, False, True)
+        staged_variant = {"ms_per_step": round(ms_staged, 5), "value": round(STEP_WEIGHT_BYTES / (ms_staged * 1e-3) / 1e9, 1),
+                          "unit": "GB/s", "frac_of_measured_hbm": round(STEP_WEIGHT_BYTES / (ms_staged * 1e-3) / 1e9 / peaks["hbm_gbs"], 4),
+                          "what": "the same step with the q/k/v, o, gate and up banks repacked offline into the B200 staged "
+                                  "layout (tessl_q4_mlx_repack_staged: two bulk copies per stage, +0.7 % bytes); down row-major; "
+                                  "results bit-identical to the headline step's (checked below)"}
+
     # ---- parity, outside the timed region ----
     rt.set_encode_only(False)
+    if staged_banks is not None:
+        y_rm = step(0).clone()
+        y_st = step(0, False, True).clone()
+        if not torch.equal(y_rm.view(torch.int32), y_st.view(torch.int32)):
+            raise SystemExit("bench: the step on staged banks differs from the step on row-major banks")
+        staged_variant["parity_vs_row_major"] = "bit-exact"
     parity = check_parity(torch, dist, nn, rt, layers[0], cpu_inputs, step, bufs, mid_full, world, rank,
                           peer_y is not None, dev)
     rt.set_encode_only(True)
@@ -461,10 +497,29 @@ def run_ours(args, rank: int, world: int, local_rank: int):
             us = time_graph(fn, iters)
             per_kernel[name] = {"us": round(us, 3), "weight_gbs": round(nbytes / us / 1e3, 1),
                                 "frac_of_measured_hbm": round(nbytes / us / 1e3 / peaks["hbm_gbs"], 4)}
+        SB = lambda i: staged_banks[i % n_layers]
+        staged_shapes = {
+            "qkv 6144x4096": (lambda i: nn.gemv_q4_mlx_simd(rt, SB(i)["qkv"], bufs["x_qkv"], qkv_b, sq, layout=nn.B200_STAGED),
+                              q4_weight_bytes(QKV, HIDDEN)),
+            "o 4096x4096": (lambda i: nn.gemv_q4_mlx_simd(rt, SB(i)["o"], bufs["x_o"], o_b, so, layout=nn.B200_STAGED),
+                            q4_weight_bytes(HIDDEN, HIDDEN)),
+            "gate_up_silu 2x12288x4096": (lambda i: nn.gemv_q4_mlx_gate_up_silu(
+                rt, SB(i)["gate"], SB(i)["up"], bufs["x_mlp"], midl_b, sg, True, layout=nn.B200_STAGED),
+                2 * q4_weight_bytes(INTER, HIDDEN)),
+            "gemv 12288x4096 (target shape)": (lambda i: nn.gemv_q4_mlx_simd(
+                rt, SB(i)["gate"], bufs["x_mlp"], gate_f32_b, nn.QuantShape(INTER, HIDDEN, GROUP), layout=nn.B200_STAGED),
+                q4_weight_bytes(INTER, HIDDEN)),
+        }
+        staged_variant["per_kernel"] = {}
+        for name, (fn, nbytes) in staged_shapes.items():
+            us = time_graph(fn, iters)
+            staged_variant["per_kernel"][name] = {"us": round(us, 3), "weight_gbs": round(nbytes / us / 1e3, 1),
+                                                  "frac_of_measured_hbm": round(nbytes / us / 1e3 / peaks["hbm_gbs"], 4)}
     rt.set_encode_only(False)
     return dict(torch=torch, dist=dist, nn=nn, rt=rt, st=st, layers=layers, acts=acts, step=step, ms_per_step=ms_per_step,
                 value=value, clocks=clocks, per_kernel=per_kernel, peaks=peaks, dev=dev,
                 launches_per_step=launches_per_step, n_layers=n_layers, parity=parity, variants=variants,
+                staged_variant=staged_variant,
                 y=y, bufs=bufs, cpu_inputs=cpu_inputs,
                 gather="peer memory, stores issued by the GEMV kernel (tessl_gemv_q4_mlx_gate_up_silu_sharded)"
                 if peer is not None else "nccl")
@@ -904,6 +959,7 @@ def main():
             "launches_per_step": 4,
         }
         line["per_kernel"] = pk
+        line["offline_repack"] = ctx["staged_variant"]
         line["e2e"] = measure_e2e(ctx, args, local_rank)
         if not args.no_extra:
             line["extra"] = measure_extra(ctx, args)

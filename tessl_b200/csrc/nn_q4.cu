@@ -296,10 +296,10 @@ struct MmaWindow {
 /// static bytes.
 constexpr uint32_t kMmaSmemBudget = 232448u - 512u;
 
-template <int SW, int WPG, int NB, bool BATCH, bool Q8 = false, int NWIN = 1, int ROWS = 16>
+template <int SW, int WPG, int NB, bool BATCH, bool Q8 = false, int NWIN = 1, int ROWS = 16, bool STAGED = false>
 Result launch_mma_one(TesslRuntime *rt, const Q4GemvParams &p, int m, const MmaWindow &w = MmaWindow{})
 {
-    auto kernel = q4m::q4_gemv_mma_kernel<SW, WPG, NB, BATCH, Q8, NWIN, ROWS>;
+    auto kernel = q4m::q4_gemv_mma_kernel<SW, WPG, NB, BATCH, Q8, NWIN, ROWS, STAGED>;
     constexpr uint32_t RPB = ROWS / NB;
     q4m::Params mp{};
     uint32_t rb = 0;
@@ -316,8 +316,8 @@ Result launch_mma_one(TesslRuntime *rt, const Q4GemvParams &p, int m, const MmaW
     mp.sb_pitch = w.sb_pitch ? w.sb_pitch : (p.cols >> p.group_shift) * 4;
     mp.x_pitch = w.x_pitch ? w.x_pitch : (Q8 ? p.cols >> 1 : p.cols);
     mp.status = rt->status_dev;
-    mp.staged = p.staged ? 1u : 0u;
-    if (p.staged && (NWIN != 1 || ROWS != 16 || BATCH || Q8)) return "q4_gemv: the staged layout runs on the one-row Q4 kernel only";
+    mp.staged = STAGED ? 1u : 0u;
+    if ((p.staged != 0) != STAGED) return "q4_gemv: the staged layout runs on the one-row Q4 kernel only";
     if (p.peer) {
         const TesslPeerGather &g = *static_cast<const TesslPeerGather *>(p.peer);
         if (BATCH || Q8 || p.nseg != 1) return "q4_gemv: a sharded launch has one bank (or one gate/up pair) and one row of x";
@@ -356,6 +356,11 @@ Result launch_mma_one(TesslRuntime *rt, const Q4GemvParams &p, int m, const MmaW
 template <int SW, int WPG>
 Result launch_mma_sw(TesslRuntime *rt, const Q4GemvParams &p, int m, int nb, const MmaWindow &w)
 {
+    if (p.staged) {
+        if (m != 1 || w.row_pitch != 0) return "q4_gemv: the staged layout runs on the one-row Q4 kernel only";
+        if (nb == 2) return launch_mma_one<SW, WPG, 2, false, false, 1, 16, true>(rt, p, m, w);
+        return launch_mma_one<SW, WPG, 1, false, false, 1, 16, true>(rt, p, m, w);
+    }
     if (nb == 2) return launch_mma_one<SW, WPG, 2, false>(rt, p, m, w);
     if (m == 1) return launch_mma_one<SW, WPG, 1, false>(rt, p, m, w);
     return launch_mma_one<SW, WPG, 1, true>(rt, p, m, w);

@@ -170,9 +170,12 @@ __device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1
 ///     long-row projection is still one launch with one fixed part.
 /// ROWS: rows per stage (16, or 14 where two stages of 16 long rows would not fit in shared memory; the
 ///     MMA's unused rows cost nothing that matters: the kernel is bound by the weight stream).
-template <int SW, int WPG, int NB, bool BATCH, bool Q8 = false, int NWIN = 1, int ROWS = 16>
+/// STAGED: the banks are in the staged layout (a compile-time choice: as a run-time one its address arithmetic
+///     cost the row-major launches 2-3 %).
+template <int SW, int WPG, int NB, bool BATCH, bool Q8 = false, int NWIN = 1, int ROWS = 16, bool STAGED = false>
 __global__ void __launch_bounds__(kThreads, TESSL_GEMV_MMA_MIN_BLOCKS) q4_gemv_mma_kernel(const Params p)
 {
+    static_assert(!STAGED || (NWIN == 1 && ROWS == 16 && !BATCH && !Q8), "staged banks: the one-row Q4 kernel");
     asm volatile("griddepcontrol.launch_dependents;");
     static_assert(NWIN == 1 || (NB == 1 && !BATCH && !Q8), "windows: one bank, one row of x, Q4");
     static_assert(ROWS % (2 * NB) == 0 && ROWS <= 16, "whole row pairs per bank");
@@ -196,7 +199,7 @@ __global__ void __launch_bounds__(kThreads, TESSL_GEMV_MMA_MIN_BLOCKS) q4_gemv_m
     // conflict on every fragment read), which costs short launches more than the copies save: the host sets
     // it from the launch's stages per SM. Pure data movement: results do not depend on it.
     const bool quads = NB == 1 && !BATCH && p.quads != 0;
-    const bool staged = NWIN == 1 && ROWS == 16 && p.staged != 0;
+    constexpr bool staged = STAGED;
     const uint32_t unit_bytes = 4 * pair_pitch + 8 * sb_row_bytes;  // one staged unit: 8 rows
     auto pair_off = [&](uint32_t gi) {
         if (staged) return (gi >> 2) * unit_bytes + (gi & 3u) * pair_pitch;
@@ -296,7 +299,7 @@ __global__ void __launch_bounds__(kThreads, TESSL_GEMV_MMA_MIN_BLOCKS) q4_gemv_m
             }
             const uint32_t nrows = min((uint32_t)RPB, seg_rows - row0);
             const uint32_t st = ring + s * stage_bytes;
-            if (staged) {
+            if constexpr (STAGED) {
                 // one bank: units 2 b and 2 b + 1 of the block; a gate/up pair: unit b of each bank
                 const Seg &sg = p.seg[cur_seg];
                 const uint32_t ua = row0 / 8, ub = NB == 1 ? ua + 1 : ua;
@@ -646,6 +649,9 @@ __global__ void __launch_bounds__(kThreads, TESSL_GEMV_MMA_MIN_BLOCKS) q4_gemv_m
         const uint32_t w_off = (k0 >> 1) + t * (G / 8);  // byte offset of the lane's first word within a row
         const uint32_t sb_off = (k0 >> p.group_shift) * 4;
 
+        // lane groups beyond the stage's row pairs (ROWS < 16) read the last pair again: their MMA rows are never stored
+        const uint32_t gp = min(g, (uint32_t)(ROWS / 2 - 1));
+        const uint32_t row_base = pair_off(gp) + w_off, sb_base = sb_pair_off(gp) + sb_off;  // within a stage
         uint32_t s = 0, ph = 0;
         for (uint32_t j = 0; j < n_local; ++j) {
             if (!mbar_wait(full(s), ph, abortp, 32)) {  // sleeping between polls leaves issue slots to the producer
@@ -658,10 +664,8 @@ __global__ void __launch_bounds__(kThreads, TESSL_GEMV_MMA_MIN_BLOCKS) q4_gemv_m
 #pragma unroll
             for (int win = 0; win < NWIN; ++win) {
             if constexpr (NWIN > 1) load_x(win), cw = cwv[win];
-            // lane groups beyond the stage's row pairs (ROWS < 16) read the last pair again: their MMA rows are never stored
-            const uint32_t gp = min(g, (uint32_t)(ROWS / 2 - 1));
-            const uint32_t row_lo = st + pair_off(gp) + w_off + win * (KW >> 1), row_hi = row_lo + row_bytes;
-            const uint32_t sb_lo = st + sb_pair_off(gp) + sb_off + win * ((KW >> p.group_shift) * 4);
+            const uint32_t row_lo = st + row_base + win * (KW >> 1), row_hi = row_lo + row_bytes;
+            const uint32_t sb_lo = st + sb_base + win * ((KW >> p.group_shift) * 4);
             const uint32_t sb_hi = sb_lo + sb_row_bytes;
             float dlo[NGS], dhi[NGS];        // M = 1: dot of MMA rows g and g + 8 per group
             // BATCH: rows g, g + 8 x columns 2 t, 2 t + 1, one accumulator per group class jj % 4 so that
