@@ -63,8 +63,8 @@ typedef struct TesslQ4MlxBank {
     TesslBuf scales_biases;
 } TesslQ4MlxBank;
 
-/* src/nn.rs:3669-3675. Only the row-major layout is built; Interleaved4 (an
- * Apple-GPU repack no Qwen3.5 path uses) is refused by name. */
+/* src/nn.rs:3669-3675. Of the reference's two layouts the row-major one is built;
+ * Interleaved4 (an Apple-GPU repack no Qwen3.5 path uses) is refused by name. */
 #define TESSL_Q4_ROW_MAJOR 0u
 #define TESSL_Q4_INTERLEAVED4 1u
 /* An offline repack for this library's GEMV kernel (the role Interleaved4 plays on
