@@ -384,6 +384,29 @@ TESSL_API int32_t tessl_checkpoint_tensor_info(const TesslCheckpoint *ck, const 
 TESSL_API int32_t tessl_mlx_quant_from_config_json(const char *text, uint32_t *bits, uint32_t *group_size, char *err,
                                          size_t err_len);
 
+/* `MlxNames::detect` (src/qwen35_q4.rs:268-293): how a checkpoint spells its
+ * tower, from its tensor names: "language_model.model." + "language_model.lm_head"
+ * (mlx-lm) or "model.language_model." + "lm_head" (Hugging Face). `*prefix` and
+ * `*head` point at constants of the library. Neither present, or both, is refused. */
+TESSL_API int32_t tessl_mlx_names_detect(const char *const *names, uint64_t n, const char **prefix, const char **head,
+                               char *err, size_t err_len);
+
+/* `NormConvention::from_conv_shape` (src/qwen35_q4.rs:296-336): a GDN layer's
+ * conv1d.weight of shape [conv_dim, 1, kernel] means the transformers layout
+ * (*convention = 0: norm weights hold w), [conv_dim, kernel, 1] the layout
+ * mlx_lm.convert writes (1: the zero-centred norms hold 1 + w, and a loader
+ * hands the kernels stored - 1). Any other shape is refused. */
+TESSL_API int32_t tessl_mlx_norm_convention_from_conv_shape(const char *tensor, const uint64_t *shape, uint32_t ndim,
+                                                  uint64_t conv_dim, uint64_t kernel, uint32_t *convention, char *err,
+                                                  size_t err_len);
+
+/* `classify_outside` (src/qwen35_q4.rs:338-373): the tensors outside the tower's
+ * prefix that no read touched: classes[i] = 0 for `mtp.*`, 1 for the vision
+ * tower (skipped on purpose, by name); anything else is refused with its count
+ * and the first eight names. */
+TESSL_API int32_t tessl_mlx_classify_outside(const char *const *names, uint64_t n, uint8_t *classes, char *err,
+                                   size_t err_len);
+
 /* `check_part` (src/qwen35_q4.rs:384-449): the three tensors of one quantized
  * [rows, cols] matrix - `X.weight` U32 [rows, cols/8], `X.scales` and `X.biases`
  * BF16 [rows, cols/64] - checked by their headers alone, before any allocation. */

@@ -110,6 +110,10 @@ SIGNATURES = {
     "tessl_checkpoint_tensor_name": (C.c_int32, [C.c_void_p, C.c_uint64, C.c_char_p, C.c_size_t] + _ERR),
     "tessl_checkpoint_tensor_info": (C.c_int32, [C.c_void_p, C.c_char_p, C.POINTER(TensorInfo)] + _ERR),
     "tessl_mlx_quant_from_config_json": (C.c_int32, [C.c_char_p, C.POINTER(_u32), C.POINTER(_u32)] + _ERR),
+    "tessl_mlx_names_detect": (C.c_int32, [C.POINTER(C.c_char_p), C.c_uint64, C.POINTER(C.c_char_p), C.POINTER(C.c_char_p)] + _ERR),
+    "tessl_mlx_norm_convention_from_conv_shape": (C.c_int32, [C.c_char_p, C.POINTER(C.c_uint64), _u32, C.c_uint64, C.c_uint64,
+                                                              C.POINTER(_u32)] + _ERR),
+    "tessl_mlx_classify_outside": (C.c_int32, [C.POINTER(C.c_char_p), C.c_uint64, C.POINTER(C.c_uint8)] + _ERR),
     "tessl_mlx_q4_check_part": (C.c_int32, [C.c_void_p, C.c_char_p, C.c_uint64, C.c_uint64] + _ERR),
     "tessl_mlx_q4_read_bank": (C.c_int32, [C.c_void_p, C.POINTER(C.c_char_p), C.POINTER(C.c_uint64), _u32, C.c_uint64,
                                            C.c_void_p, C.c_uint64, C.c_void_p, C.c_uint64] + _ERR),

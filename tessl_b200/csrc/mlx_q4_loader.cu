@@ -550,6 +550,74 @@ Result quant_from_config_json(const char *text, uint32_t *bits, uint32_t *group_
     return ok();
 }
 
+std::string quoted_list(const std::vector<std::string> &v)
+{
+    std::string t = "[";
+    for (size_t i = 0; i < v.size(); ++i) t += (i ? ", \"" : "\"") + v[i] + "\"";
+    return t + "]";
+}
+
+bool starts_with(const char *s, const char *prefix) { return std::strncmp(s, prefix, std::strlen(prefix)) == 0; }
+
+constexpr const char *kMlxPrefix = "language_model.model.", *kMlxHead = "language_model.lm_head";
+constexpr const char *kHfPrefix = "model.language_model.", *kHfHead = "lm_head";
+
+/// `MlxNames::detect` (src/qwen35_q4.rs:268-293): which spelling of the tower the names use; both is refused.
+Result names_detect(const char *const *names, uint64_t n, const char **prefix, const char **head)
+{
+    bool mlx = false, hf = false;
+    for (uint64_t i = 0; i < n; ++i) {
+        if (!names[i]) return "MlxNames::detect: null name";
+        mlx |= starts_with(names[i], kMlxPrefix);
+        hf |= starts_with(names[i], kHfPrefix);
+    }
+    if (mlx && hf)
+        return "checkpoint conventions: tensors under both \"language_model.model.\" and \"model.language_model.\"";
+    if (!mlx && !hf)
+        return "no tensor under \"language_model.model.\" (mlx-lm) or \"model.language_model.\" (Hugging Face): not a "
+               "Qwen3.5 checkpoint";
+    *prefix = mlx ? kMlxPrefix : kHfPrefix, *head = mlx ? kMlxHead : kHfHead;
+    return ok();
+}
+
+/// `NormConvention::from_conv_shape` (src/qwen35_q4.rs:323-336): [conv_dim, 1, k] is the transformers layout (0),
+/// [conv_dim, k, 1] the one `mlx_lm.convert` writes, whose zero-centred norms hold 1 + w (1).
+Result norm_convention_from_conv_shape(const char *tensor, const uint64_t *shape, uint32_t ndim, uint64_t conv_dim,
+                                       uint64_t kernel, uint32_t *convention)
+{
+    const std::vector<uint64_t> got(shape, shape + ndim), hf = {conv_dim, 1, kernel}, mlx = {conv_dim, kernel, 1};
+    if (got == hf) return *convention = 0, ok();
+    if (got == mlx) return *convention = 1, ok();
+    return fmt("%s: shape %s, expected %s (4-bit packs eight values per U32 word; a different width means other bits)",
+               tensor, shape_text(got).c_str(), shape_text(hf).c_str());
+}
+
+/// `classify_outside` (src/qwen35_q4.rs:350-373): tensors outside the tower that no read touched are either
+/// skipped on purpose and by name - `mtp.*` (class 0), the vision tower (class 1) - or refused.
+Result classify_outside(const char *const *names, uint64_t n, uint8_t *classes)
+{
+    static const char *kVision[4] = {"vision_tower.", "model.visual.", "visual.", "model.vision_tower."};
+    std::vector<std::string> other;
+    for (uint64_t i = 0; i < n; ++i) {
+        if (!names[i]) return "classify_outside: null name";
+        bool vision = false;
+        for (const char *p : kVision) vision |= starts_with(names[i], p);
+        if (starts_with(names[i], "mtp.")) {
+            classes[i] = 0;
+        } else if (vision) {
+            classes[i] = 1;
+        } else {
+            classes[i] = 255;
+            other.push_back(names[i]);
+        }
+    }
+    if (other.empty()) return ok();
+    const size_t count = other.size();
+    if (other.size() > 8) other.resize(8);
+    return fmt("%zu tensor(s) outside the tower that are neither its head nor mtp.* / the vision tower: %s", count,
+               quoted_list(other).c_str());
+}
+
 void put_err(char *err, size_t err_len, const std::string &msg)
 {
     if (!err || err_len == 0) return;
@@ -636,6 +704,32 @@ int32_t tessl_mlx_quant_from_config_json(const char *text, uint32_t *bits, uint3
     return tessl::host_guarded(err, err_len, [&]() -> Result {
         if (!bits || !group_size) return "tessl_mlx_quant_from_config_json: null out";
         return tessl::quant_from_config_json(text, bits, group_size);
+    });
+}
+
+int32_t tessl_mlx_names_detect(const char *const *names, uint64_t n, const char **prefix, const char **head, char *err,
+                               size_t err_len)
+{
+    return tessl::host_guarded(err, err_len, [&]() -> Result {
+        if ((n && !names) || !prefix || !head) return "tessl_mlx_names_detect: null argument";
+        return tessl::names_detect(names, n, prefix, head);
+    });
+}
+
+int32_t tessl_mlx_norm_convention_from_conv_shape(const char *tensor, const uint64_t *shape, uint32_t ndim, uint64_t conv_dim,
+                                                  uint64_t kernel, uint32_t *convention, char *err, size_t err_len)
+{
+    return tessl::host_guarded(err, err_len, [&]() -> Result {
+        if (!tensor || (ndim && !shape) || !convention) return "tessl_mlx_norm_convention_from_conv_shape: null argument";
+        return tessl::norm_convention_from_conv_shape(tensor, shape, ndim, conv_dim, kernel, convention);
+    });
+}
+
+int32_t tessl_mlx_classify_outside(const char *const *names, uint64_t n, uint8_t *classes, char *err, size_t err_len)
+{
+    return tessl::host_guarded(err, err_len, [&]() -> Result {
+        if (n && (!names || !classes)) return "tessl_mlx_classify_outside: null argument";
+        return tessl::classify_outside(names, n, classes);
     });
 }
 

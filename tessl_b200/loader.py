@@ -130,3 +130,51 @@ class Checkpoint:
     def mlx_q4(self, rt: Runtime, prefix: str, parts: Sequence, cols: int) -> Q4MlxBank:
         """`Loader::mlx_q4`: parts named by suffix under a layer prefix, e.g. ("self_attn.q_proj", rows)."""
         return self.mlx_q4_named(rt, [(f"{prefix}.{s}.weight", r) for s, r in parts], cols)
+
+
+@dataclass(frozen=True)
+class MlxNames:
+    """How a checkpoint spells its tower (`MlxNames`, src/qwen35_q4.rs:258-293 of the reference)."""
+
+    prefix: str
+    head: str
+
+    @staticmethod
+    def detect(names: Sequence) -> "MlxNames":
+        arr = (C.c_char_p * len(names))(*[n.encode("utf-8") for n in names])
+        prefix, head = C.c_char_p(), C.c_char_p()
+        capi.call("tessl_mlx_names_detect", arr, len(names), C.byref(prefix), C.byref(head))
+        return MlxNames(prefix.value.decode("ascii"), head.value.decode("ascii"))
+
+
+class NormConvention:
+    """Whether the norm weights hold w (`HF`) or 1 + w (`MLX_SHIFTED`), read off a GDN layer's conv1d.weight
+    (`NormConvention`, src/qwen35_q4.rs:296-336 of the reference)."""
+
+    HF, MLX_SHIFTED = 0, 1
+
+    @staticmethod
+    def from_conv_shape(tensor: str, shape: Sequence, conv_dim: int, kernel: int) -> int:
+        arr = (C.c_uint64 * len(shape))(*[int(d) for d in shape])
+        out = C.c_uint32(0)
+        capi.call("tessl_mlx_norm_convention_from_conv_shape", tensor.encode("utf-8"), arr, len(shape), conv_dim, kernel,
+                  C.byref(out))
+        return out.value
+
+    @staticmethod
+    def conv_shape(convention: int, conv_dim: int, kernel: int) -> tuple:
+        return (conv_dim, 1, kernel) if convention == NormConvention.HF else (conv_dim, kernel, 1)
+
+    @staticmethod
+    def unshift(convention: int, stored) -> np.float32:
+        """The value to hand a kernel that adds 1 itself, from a stored norm weight (f32 arithmetic)."""
+        s = np.float32(stored)
+        return s if convention == NormConvention.HF else np.float32(s - np.float32(1.0))
+
+
+def classify_outside(unread: Sequence) -> dict:
+    """`classify_outside` (src/qwen35_q4.rs:338-373): {"mtp": [...], "vision": [...]}; anything else is refused."""
+    arr = (C.c_char_p * len(unread))(*[n.encode("utf-8") for n in unread])
+    classes = (C.c_uint8 * max(len(unread), 1))()
+    capi.call("tessl_mlx_classify_outside", arr, len(unread), classes)
+    return {"mtp": [n for n, c in zip(unread, classes) if c == 0], "vision": [n for n, c in zip(unread, classes) if c == 1]}

@@ -277,3 +277,55 @@ def test_the_largest_bf16_finite_values_load(tmp_path):
     with _variant(tmp_path, edit) as v:
         _, pairs = v.read_mlx_q4([(mc.PREFIX + ".self_attn.k_proj.weight", 64)], 128)
     assert pairs[0, 0, 0] == big[0] and pairs[0, 1, 0] == big[1]
+
+
+# ------------------------------------------------- names and conventions ---
+# tests/qwen35_mlx_q4_layout.rs:212-330 of the reference project
+
+def test_the_key_spelling_is_detected_and_ambiguity_refused():
+    mlx = ["language_model.model.embed_tokens.weight", "language_model.lm_head.weight"]
+    assert loader.MlxNames.detect(mlx) == loader.MlxNames("language_model.model.", "language_model.lm_head")
+    hf = ["model.language_model.embed_tokens.weight", "lm_head.weight"]
+    assert loader.MlxNames.detect(hf) == loader.MlxNames("model.language_model.", "lm_head")
+    assert "not a Qwen3.5 checkpoint" in refused(loader.MlxNames.detect, ["model.visual.x"])
+    assert "not a Qwen3.5 checkpoint" in refused(loader.MlxNames.detect, [])
+    e = refused(loader.MlxNames.detect, [mlx[0], hf[0]])
+    assert e.startswith("checkpoint conventions:") and "both" in e
+
+
+def test_the_conv_layout_says_which_norm_convention_the_checkpoint_is_in():
+    c, k = 6144, 4
+    NC = loader.NormConvention
+    assert NC.from_conv_shape("conv", [c, 1, k], c, k) == NC.HF
+    assert NC.from_conv_shape("conv", [c, k, 1], c, k) == NC.MLX_SHIFTED
+    e = refused(NC.from_conv_shape, "conv", [c, 2, 2], c, k)
+    assert e.startswith("conv: shape [6144, 2, 2], expected [6144, 1, 4]")
+    assert "shape [6144, 4]" in refused(NC.from_conv_shape, "conv", [c, k], c, k)
+    # the kernels add 1 themselves, so the shifted convention is undone, and exactly: a bf16 value near 1 minus 1 is
+    # exact in f32, and adding the 1 back gives the stored value again bit for bit
+    for stored in (0.0, 0.5, 1.0, 1.0078125, 1.75, 2.5, 33.0, -0.25, 0.00390625):
+        w = NC.unshift(NC.MLX_SHIFTED, stored)
+        assert (np.float32(1.0) + w).view(np.uint32) == np.float32(stored).view(np.uint32), stored
+        assert NC.unshift(NC.HF, stored).view(np.uint32) == np.float32(stored).view(np.uint32)
+    assert NC.conv_shape(NC.MLX_SHIFTED, c, k) == (c, k, 1) and NC.conv_shape(NC.HF, c, k) == (c, 1, k)
+
+
+def test_mtp_and_vision_tensors_are_skipped_by_name_and_counted():
+    unread = ["mtp.fc.weight", "mtp.layers.0.mlp.down_proj.weight", "mtp.norm.weight",
+              "model.visual.blocks.0.attn.qkv.weight", "model.visual.blocks.1.attn.qkv.weight", "vision_tower.merger.weight"]
+    assert loader.classify_outside(unread) == {"mtp": unread[:3], "vision": unread[3:]}
+    assert loader.classify_outside([]) == {"mtp": [], "vision": []}
+
+
+def test_any_other_tensor_outside_the_tower_is_refused():
+    e = refused(loader.classify_outside, ["mtp.fc.weight", "lm_head.bias", "audio_tower.x"])
+    assert e.startswith("2 tensor(s) outside the tower") and '["lm_head.bias", "audio_tower.x"]' in e
+    many = [f"stray.{i}" for i in range(11)]
+    e = refused(loader.classify_outside, many)
+    assert e.startswith("11 tensor(s)") and '"stray.7"' in e and '"stray.8"' not in e
+
+
+def test_a_drafter_checkpoint_without_a_tower_prefix_is_not_mistaken_for_a_tower():
+    # unprefixed names such as a stand-alone multi-token-prediction drafter carries: fails closed
+    names = ["fc.biases", "fc.scales", "fc.weight", "layers.0.mlp.down_proj.weight", "norm.weight", "pre_fc_norm_hidden.weight"]
+    assert "not a Qwen3.5 checkpoint" in refused(loader.MlxNames.detect, names)
