@@ -193,11 +193,11 @@ __global__ void __launch_bounds__(kThreads, TESSL_GEMV_MMA_MIN_BLOCKS) q4_gemv_m
     // copy more than per byte, and sixteen 2 KB copies per stage bounded the stream. Pairs sit 32 bytes
     // past a multiple of 128 apart (bank-conflict-free fragment reads).
     const uint32_t pair_pitch = 2 * row_bytes + kRowPad;
-    // Long streams (`quads`): two pairs back to back so that one copy fetches four rows - eight copies of 4 KB
-    // per stage still cost the copy unit more than the bytes do, four of 8 KB reach the pure read rate - with
-    // the quads 32 bytes past a multiple of 128 apart. The two pairs of a quad then share banks (a two-way
-    // conflict on every fragment read), which costs short launches more than the copies save: the host sets
-    // it from the launch's stages per SM. Pure data movement: results do not depend on it.
+    // `quads` (one bank, dense rows, one row of x): two pairs back to back so that one copy fetches four rows -
+    // eight copies of 4 KB per stage still cost the copy unit more than the bytes do, four of 8 KB reach the
+    // pure read rate on a long stream - with the quads 32 bytes past a multiple of 128 apart. The two pairs of
+    // a quad then share banks (a two-way conflict on every fragment read), which the copies more than pay
+    // for at every launch size measured. Pure data movement: results do not depend on it.
     const bool quads = NB == 1 && !BATCH && p.quads != 0;
     constexpr bool staged = STAGED;
     const uint32_t unit_bytes = 4 * pair_pitch + 8 * sb_row_bytes;  // one staged unit: 8 rows
