@@ -340,7 +340,7 @@ Result launch_mma_one(TesslRuntime *rt, const Q4GemvParams &p, int m, const MmaW
     const uint32_t grid = std::min<uint32_t>(rb, (uint32_t)rt->sm_count);
     // four rows per bulk copy wherever two row pairs are adjacent in memory (one bank, dense rows): 151936 x 4096
     // 58.8 -> 52.7 us, 6144 x 4096 5.30 -> 5.05 us, 12288 x 4096 8.00 -> 7.90 us on one box, back to back
-    mp.quads = (NB == 1 && !BATCH && NWIN == 1 && w.row_pitch == 0 && !p.staged) ? 1u : 0u;
+    mp.quads = (!BATCH && NWIN == 1 && w.row_pitch == 0 && !p.staged) ? 1u : 0u;
     cudaLaunchConfig_t lc{};
     lc.gridDim = dim3(grid), lc.blockDim = dim3(q4m::kThreads), lc.dynamicSmemBytes = smem;
     lc.stream = rt->stream;

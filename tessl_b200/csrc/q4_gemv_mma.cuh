@@ -193,12 +193,12 @@ __global__ void __launch_bounds__(kThreads, TESSL_GEMV_MMA_MIN_BLOCKS) q4_gemv_m
     // copy more than per byte, and sixteen 2 KB copies per stage bounded the stream. Pairs sit 32 bytes
     // past a multiple of 128 apart (bank-conflict-free fragment reads).
     const uint32_t pair_pitch = 2 * row_bytes + kRowPad;
-    // `quads` (one bank, dense rows, one row of x): two pairs back to back so that one copy fetches four rows -
+    // `quads` (dense rows, one row of x): two pairs of a bank back to back so that one copy fetches four rows -
     // eight copies of 4 KB per stage still cost the copy unit more than the bytes do, four of 8 KB reach the
     // pure read rate on a long stream - with the quads 32 bytes past a multiple of 128 apart. The two pairs of
     // a quad then share banks (a two-way conflict on every fragment read), which the copies more than pay
     // for at every launch size measured. Pure data movement: results do not depend on it.
-    const bool quads = NB == 1 && !BATCH && p.quads != 0;
+    const bool quads = !BATCH && p.quads != 0;
     constexpr bool staged = STAGED;
     const uint32_t unit_bytes = 4 * pair_pitch + 8 * sb_row_bytes;  // one staged unit: 8 rows
     auto pair_off = [&](uint32_t gi) {
@@ -325,7 +325,8 @@ __global__ void __launch_bounds__(kThreads, TESSL_GEMV_MMA_MIN_BLOCKS) q4_gemv_m
                     }
                 } else if (pair_copy) {
                     if (quads && nrows == RPB) {
-                        if (mhi == 0 && (mg & 1u) == 0 && mg < HP) bulk_g2s(st + my_dst, src, (mg + 1 < HP ? 4 : 2) * row_bytes, full(s));
+                        if (mhi == 0 && (mg & 1u) == 0 && mg < HP * NB)
+                            bulk_g2s(st + my_dst, src, ((mg % HP) + 1 < HP ? 4 : 2) * row_bytes, full(s));
                     } else if (mhi == 0 && my_r < nrows) bulk_g2s(st + my_dst, src, my_r + 1 < nrows ? 2 * row_bytes : row_bytes, full(s));
                 } else if (my_r < nrows) {
                     bulk_g2s(st + my_dst, src, row_bytes, full(s));
