@@ -295,6 +295,32 @@ TESSL_API int32_t tessl_gemv_q4_mlx_gate_up_silu_sharded(TesslRuntime *rt, Tessl
                                                TesslBuf x_bf16, const TesslPeerGather *gather, TesslQuantShape shape,
                                                uint32_t mid_as_bf16, char *err, size_t err_len);
 
+/* The same two launches without the last wait: the kernel stores its outputs to
+ * every rank, tells the peers that they are complete and ends; it does NOT wait
+ * for the peers' slices. The reader of the gathered vector does that instead -
+ * tessl_gemv_q4_mlx_simd_gathered inside its kernel, behind that kernel's own
+ * weight prefetch, or tessl_peer_wait as a launch of its own before any other
+ * reader - so the NVLink round trip is no longer exposed between the two
+ * launches. After a deferred call, buffers[rank] must not be read by anything
+ * else first. NO COUNTERPART IN THE REFERENCE. */
+TESSL_API int32_t tessl_gemv_q4_mlx_simd_sharded_deferred(TesslRuntime *rt, TesslQ4MlxBank bank, TesslBuf x_bf16,
+                                                const TesslPeerGather *gather, TesslQuantShape shape,
+                                                uint32_t y_as_bf16, char *err, size_t err_len);
+TESSL_API int32_t tessl_gemv_q4_mlx_gate_up_silu_sharded_deferred(TesslRuntime *rt, TesslQ4MlxBank gate, TesslQ4MlxBank up,
+                                                        TesslBuf x_bf16, const TesslPeerGather *gather,
+                                                        TesslQuantShape shape, uint32_t mid_as_bf16, char *err,
+                                                        size_t err_len);
+/* tessl_gemv_q4_mlx_simd[_bf16] whose x is the gathered vector buffers[rank]
+ * (bf16, world * bytes_per_rank bytes) of `gather`: before reading x the kernel
+ * waits, bounded like every peer wait, until every peer's completion flag has
+ * reached this rank's call counter. Correct after a deferred and after a waiting
+ * exchange alike. */
+TESSL_API int32_t tessl_gemv_q4_mlx_simd_gathered(TesslRuntime *rt, TesslQ4MlxBank bank, const TesslPeerGather *gather,
+                                        TesslBuf y, TesslQuantShape shape, const TesslBuf *resid, uint32_t y_as_bf16,
+                                        char *err, size_t err_len);
+/* The deferred wait as a launch of its own, for any other reader of buffers[rank]. */
+TESSL_API int32_t tessl_peer_wait(TesslRuntime *rt, const TesslPeerGather *gather, char *err, size_t err_len);
+
 /* `Q4Weight::matmul` (src/qwen35_q4.rs:518-561): the M-dispatch policy over one
  * bank of group size 64. m == 0 is a no-op, 1 the GEMV, 2..=8 the small-batch
  * kernel, more the tensor-core GEMM (which refuses a residual). x is bf16

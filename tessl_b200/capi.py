@@ -93,6 +93,12 @@ SIGNATURES = {
     "tessl_gemm_q4_mlx_tensorops_bf16": (C.c_int32, [_RT, Q4MlxBank, Buf, Buf, QuantShape, _u32] + _ERR),
     "tessl_gemm_q4_mlx_tensorops_noalloc": (C.c_int32, [_RT, Q4MlxBank, Buf, Buf, QuantShape, _u32] + _ERR),
     "tessl_peer_gather": (C.c_int32, [_RT, C.POINTER(PeerGather)] + _ERR),
+    "tessl_gemv_q4_mlx_simd_sharded_deferred": (C.c_int32, [_RT, Q4MlxBank, Buf, C.POINTER(PeerGather), QuantShape, _u32] + _ERR),
+    "tessl_gemv_q4_mlx_gate_up_silu_sharded_deferred": (C.c_int32, [_RT, Q4MlxBank, Q4MlxBank, Buf, C.POINTER(PeerGather),
+                                                                    QuantShape, _u32] + _ERR),
+    "tessl_gemv_q4_mlx_simd_gathered": (C.c_int32, [_RT, Q4MlxBank, C.POINTER(PeerGather), Buf, QuantShape, C.POINTER(Buf),
+                                                    _u32] + _ERR),
+    "tessl_peer_wait": (C.c_int32, [_RT, C.POINTER(PeerGather)] + _ERR),
     "tessl_gemv_q4_mlx_simd_sharded": (C.c_int32, [_RT, Q4MlxBank, Buf, C.POINTER(PeerGather), QuantShape, _u32] + _ERR),
     "tessl_gemv_q4_mlx_gate_up_silu_sharded": (C.c_int32, [_RT, Q4MlxBank, Q4MlxBank, Buf, C.POINTER(PeerGather), QuantShape,
                                                            _u32] + _ERR),

@@ -469,6 +469,45 @@ int32_t tessl_gemv_q4_mlx_simd_sharded(TesslRuntime *rt, TesslQ4MlxBank bank, Te
     });
 }
 
+int32_t tessl_gemv_q4_mlx_simd_sharded_deferred(TesslRuntime *rt, TesslQ4MlxBank bank, TesslBuf x_bf16,
+                                                const TesslPeerGather *gather, TesslQuantShape shape, uint32_t y_as_bf16,
+                                                char *err, size_t err_len)
+{
+    return guarded(rt, err, err_len, true, [&]() -> tessl::Result {
+        if (!gather) return "gemv_q4_mlx_simd_sharded_deferred: null descriptor";
+        return tessl::nn::gemv_q4_mlx_simd_sharded(rt, bank, x_bf16, *gather, shape, y_as_bf16 != 0, true);
+    });
+}
+
+int32_t tessl_gemv_q4_mlx_gate_up_silu_sharded_deferred(TesslRuntime *rt, TesslQ4MlxBank gate, TesslQ4MlxBank up,
+                                                        TesslBuf x_bf16, const TesslPeerGather *gather, TesslQuantShape shape,
+                                                        uint32_t mid_as_bf16, char *err, size_t err_len)
+{
+    return guarded(rt, err, err_len, true, [&]() -> tessl::Result {
+        if (!gather) return "gemv_q4_mlx_gate_up_silu_sharded_deferred: null descriptor";
+        return tessl::nn::gemv_q4_mlx_gate_up_silu_sharded(rt, gate, up, x_bf16, *gather, shape, mid_as_bf16 != 0, true);
+    });
+}
+
+int32_t tessl_gemv_q4_mlx_simd_gathered(TesslRuntime *rt, TesslQ4MlxBank bank, const TesslPeerGather *gather, TesslBuf y,
+                                        TesslQuantShape shape, const TesslBuf *resid, uint32_t y_as_bf16, char *err,
+                                        size_t err_len)
+{
+    return guarded(rt, err, err_len, true, [&]() -> tessl::Result {
+        if (!gather) return "gemv_q4_mlx_simd_gathered: null descriptor";
+        return tessl::nn::gemv_q4_mlx_simd_gathered(rt, bank, *gather, y, shape, resid,
+                                                    y_as_bf16 ? tessl::nn::OUT_BF16 : tessl::nn::OUT_F32);
+    });
+}
+
+int32_t tessl_peer_wait(TesslRuntime *rt, const TesslPeerGather *gather, char *err, size_t err_len)
+{
+    return guarded(rt, err, err_len, true, [&]() -> tessl::Result {
+        if (!gather) return "peer_wait: null descriptor";
+        return tessl::nn::peer_wait(rt, *gather);
+    });
+}
+
 int32_t tessl_gemv_q4_mlx_gate_up_silu_sharded(TesslRuntime *rt, TesslQ4MlxBank gate, TesslQ4MlxBank up, TesslBuf x_bf16,
                                                const TesslPeerGather *gather, TesslQuantShape shape, uint32_t mid_as_bf16,
                                                char *err, size_t err_len)

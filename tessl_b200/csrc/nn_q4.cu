@@ -327,6 +327,14 @@ Result launch_mma_one(TesslRuntime *rt, const Q4GemvParams &p, int m, const MmaW
         }
         mp.peer.rank = g.rank, mp.peer.world = g.world;
         mp.peer.wait_clocks = rt->peer_wait_clocks ? (long long)rt->peer_wait_clocks : kPeerWaitClocks;
+        mp.peer.defer = p.peer_defer ? 1u : 0u;
+    }
+    if (p.xwait) {
+        const TesslPeerGather &g = *static_cast<const TesslPeerGather *>(p.xwait);
+        if (BATCH || Q8) return "q4_gemv: a gathered x is one row";
+        mp.xwait.flags = g.flags[g.rank];
+        mp.xwait.rank = g.rank, mp.xwait.world = g.world;
+        mp.xwait.wait_clocks = rt->peer_wait_clocks ? (long long)rt->peer_wait_clocks : kPeerWaitClocks;
     }
     const uint32_t gpr = p.cols >> p.group_shift;
     const uint32_t part = BATCH ? q4m::kConsumers * 16 * 8 * 4 : q4m::kConsumers * 16 * 4;
@@ -466,6 +474,13 @@ bool tma_ok(const Q4GemvParams &p)
 /// summation order never depends on the launch) and the matching instantiation.
 Result launch_q4_gemv(TesslRuntime *rt, Q4GemvParams p, int m, int nb)
 {
+    if (p.xwait && !(m == 1 && (mma_ok(p) || mma_long_ok(p, m)))) {
+        // a width the tensor-core kernel does not take: the wait as a launch of its own, then whichever kernel serves it
+        const TesslPeerGather *g = static_cast<const TesslPeerGather *>(p.xwait);
+        p.xwait = nullptr;
+        TESSL_TRY(nn::peer_wait(rt, *g));
+        return launch_q4_gemv(rt, p, m, nb);
+    }
     if (p.peer && !(m == 1 && (mma_ok(p) || (mma_long_ok(p, m) && nb == 1)))) {
         // shapes the tensor-core kernel does not take: the slice by whichever kernel serves it, then the
         // stand-alone exchange (same flag words, same result)
@@ -741,7 +756,7 @@ static Result sharded_out(const TesslPeerGather &g, const char *entry, uint64_t 
 }
 
 Result gemv_q4_mlx_simd_sharded(TesslRuntime *rt, const TesslQ4MlxBank &bank, const TesslBuf &x_bf16,
-                                const TesslPeerGather &gather, const TesslQuantShape &shape, bool y_as_bf16)
+                                const TesslPeerGather &gather, const TesslQuantShape &shape, bool y_as_bf16, bool defer)
 {
     const char *entry = "gemv_q4_mlx_simd_sharded";
     TesslBuf y{};
@@ -763,12 +778,42 @@ Result gemv_q4_mlx_simd_sharded(TesslRuntime *rt, const TesslQ4MlxBank &bank, co
     p.epi = EPI_STORE;
     p.out_bf16 = y_as_bf16;
     p.peer = gather.world > 1 ? &gather : nullptr;
+    p.peer_defer = defer;
+    return launch_q4_gemv(rt, p, 1, 1);
+}
+
+Result gemv_q4_mlx_simd_gathered(TesslRuntime *rt, const TesslQ4MlxBank &bank, const TesslPeerGather &gather,
+                                 const TesslBuf &y, const TesslQuantShape &shape, const TesslBuf *resid, OutKind out)
+{
+    const char *entry = "gemv_q4_mlx_simd_gathered";
+    TESSL_TRY(peer_gather_validate(gather, entry));
+    TesslBuf x{};
+    x.ptr = gather.buffers[gather.rank];
+    x.nbytes = (uint64_t)gather.world * gather.bytes_per_rank;
+    TESSL_TRY(q4_bank_validate(bank, shape, entry));
+    TESSL_TRY(require(x, shape.cols, 2, std::string(entry) + " gathered x"));
+    TESSL_TRY(require(y, shape.rows, out == OUT_BF16 ? 2 : 4, std::string(entry) + " y"));
+    if (resid) TESSL_TRY(require(*resid, shape.rows, 4, std::string(entry) + " resid"));
+    if (shape.rows == 0) return ok();
+    const Named writes[] = {{"y", &y}};
+    const Named reads[] = {{"packed", &bank.packed}, {"scales_biases", &bank.scales_biases}, {"gathered x", &x}};
+    TESSL_TRY(require_disjoint_writes(entry, writes, 1, reads, 3));
+    TESSL_TRY(check_alignment(bank, entry));
+    Q4GemvParams p{};
+    p.seg[0] = make_seg(bank, nullptr, y, resid, shape.rows);
+    p.nseg = 1;
+    p.x = static_cast<const uint16_t *>(x.ptr);
+    p.cols = shape.cols;
+    p.group_shift = log2_u32(shape.group_size);
+    p.epi = resid ? EPI_ADD_RESID : EPI_STORE;
+    p.out_bf16 = out == OUT_BF16;
+    p.xwait = gather.world > 1 ? &gather : nullptr;
     return launch_q4_gemv(rt, p, 1, 1);
 }
 
 Result gemv_q4_mlx_gate_up_silu_sharded(TesslRuntime *rt, const TesslQ4MlxBank &gate, const TesslQ4MlxBank &up,
                                         const TesslBuf &x, const TesslPeerGather &gather, const TesslQuantShape &shape,
-                                        bool mid_as_bf16)
+                                        bool mid_as_bf16, bool defer)
 {
     const char *entry = "gemv_q4_mlx_gate_up_silu_sharded";
     TesslBuf mid{};
@@ -796,6 +841,7 @@ Result gemv_q4_mlx_gate_up_silu_sharded(TesslRuntime *rt, const TesslQ4MlxBank &
     p.epi = EPI_GATE_UP_SILU;
     p.out_bf16 = mid_as_bf16;
     p.peer = gather.world > 1 ? &gather : nullptr;
+    p.peer_defer = defer;
     return launch_q4_gemv(rt, p, 1, 2);
 }
 

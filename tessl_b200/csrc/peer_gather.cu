@@ -102,9 +102,46 @@ __global__ void __launch_bounds__(1024, 1) peer_gather_kernel(const PeerGatherPa
     if (threadIdx.x == 0) mine[17] = 0, mine[16] = seq;
 }
 
+/// The wait that a deferred exchange left to its reader, as a launch of its own (for readers that are not the
+/// tensor-core GEMV, which does it itself): every peer's completion flag has reached this rank's call counter.
+__global__ void peer_wait_kernel(const uint32_t *mine, uint32_t rank, uint32_t world, long long wait_clocks, uint32_t *status)
+{
+    asm volatile("griddepcontrol.launch_dependents;");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    const uint32_t seq = *(volatile const uint32_t *)(mine + 16);
+    if (threadIdx.x < world && threadIdx.x != rank) {
+        const long long t0 = clock64();
+        while ((int32_t)(ld_acquire_sys(mine + 8 + threadIdx.x) - seq) < 0) {
+            if (clock64() - t0 > wait_clocks) {
+                *(volatile uint32_t *)status = (0x50u << 24) | (5u << 16) | threadIdx.x;
+                break;
+            }
+            __nanosleep(64);
+        }
+    }
+}
+
 }  // namespace
 
 namespace nn {
+
+Result peer_wait(TesslRuntime *rt, const TesslPeerGather &g)
+{
+    TESSL_TRY(peer_gather_validate(g, "peer_wait"));
+    if (g.world == 1) return ok();
+    cudaLaunchConfig_t lc{};
+    lc.gridDim = dim3(1), lc.blockDim = dim3(32), lc.dynamicSmemBytes = 0;
+    lc.stream = rt->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    lc.attrs = attr, lc.numAttrs = 1;
+    const long long clocks = rt->peer_wait_clocks ? (long long)rt->peer_wait_clocks : kPeerWaitClocks;
+    const cudaError_t e = cudaLaunchKernelEx(&lc, peer_wait_kernel, (const uint32_t *)g.flags[g.rank], g.rank, g.world, clocks,
+                                             rt->status_dev);
+    rt->dispatch_count += 1;
+    return cuda_check(rt, e, "peer_wait launch");
+}
 
 Result peer_gather(TesslRuntime *rt, const TesslPeerGather &g)
 {

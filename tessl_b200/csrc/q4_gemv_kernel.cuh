@@ -64,6 +64,8 @@ struct Params {
     // Host side only: the TesslPeerGather of a column-sharded launch whose kernel exchanges its own
     // outputs (q4_gemv_mma.cuh), else null. Kernels other than that one never read it.
     const void *peer;
+    int peer_defer;     // with `peer`: tell the peers, do not wait for them (the reader of the gathered vector does)
+    const void *xwait;  // a TesslPeerGather whose buffer is x and whose last exchange was deferred, else null
     // Host side only: the banks are in the staged layout (units of 8 rows in the tensor-core kernel's
     // shared-memory form); only that kernel takes them.
     int staged;

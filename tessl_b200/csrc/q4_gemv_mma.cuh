@@ -83,6 +83,17 @@ struct Peer {
     uint32_t *flags[8];  // flag words of every rank
     uint32_t rank, world;
     long long wait_clocks;  // bound of every wait for a peer
+    // 1: the launch tells its peers that its outputs are complete but does not wait for theirs; the kernel that
+    // reads the gathered vector does (`XWait`), behind its own weight prefetch.
+    uint32_t defer;
+};
+
+/// The activations are a gather buffer whose last exchange was launched with `defer`: before reading x, wait
+/// until every peer's completion flag has reached this rank's call counter (world <= 1: nothing to wait for).
+struct XWait {
+    const uint32_t *flags;  // this rank's flag words
+    uint32_t rank, world;
+    long long wait_clocks;
 };
 
 struct Params {
@@ -109,6 +120,7 @@ struct Params {
     uint32_t staged;
     uint32_t *status;
     Peer peer;
+    XWait xwait;
 };
 
 __device__ __forceinline__ void st_release_sys(uint32_t *p, uint32_t v)
@@ -122,17 +134,18 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t *p)
     return v;
 }
 
-/// Lane t < world (t != rank) of the calling warp waits until flag word `base + t` of this rank reaches
+/// Lane t < world (t != rank) of the calling warp waits until flag word `base + t` of this rank (`mine`) reaches
 /// `seq`; false (and a status word, role 0x50 like the stand-alone gather) when the bound runs out.
-__device__ __forceinline__ bool peer_wait(const Peer &pe, uint32_t *status, uint32_t base, uint32_t seq, uint32_t code)
+__device__ __forceinline__ bool peer_wait(const uint32_t *mine, uint32_t rank, uint32_t world, long long wait_clocks,
+                                          uint32_t *status, uint32_t base, uint32_t seq, uint32_t code)
 {
     const uint32_t lane = threadIdx.x & 31;
     bool ok_ = true;
-    if (lane < pe.world && lane != pe.rank) {
-        const uint32_t *f = pe.flags[pe.rank] + base + lane;
+    if (lane < world && lane != rank) {
+        const uint32_t *f = mine + base + lane;
         const long long t0 = clock64();
         while ((int32_t)(ld_acquire_sys(f) - seq) < 0) {
-            if (clock64() - t0 > pe.wait_clocks) {
+            if (clock64() - t0 > wait_clocks) {
                 *(volatile uint32_t *)status = (0x50u << 24) | (code << 16) | lane;
                 ok_ = false;
                 break;
@@ -142,7 +155,6 @@ __device__ __forceinline__ bool peer_wait(const Peer &pe, uint32_t *status, uint
     }
     return __all_sync(0xffffffffu, ok_);
 }
-
 
 __device__ __forceinline__ uint2 lds64(uint32_t addr)
 {
@@ -359,7 +371,8 @@ __global__ void __launch_bounds__(kThreads, TESSL_GEMV_MMA_MIN_BLOCKS) q4_gemv_m
             seq = *(volatile uint32_t *)(p.peer.flags[p.peer.rank] + 16) + 1;  // advanced by the call's last block only
             if (blockIdx.x == 0 && (uint32_t)lane < p.peer.world && (uint32_t)lane != p.peer.rank)
                 st_release_sys(p.peer.flags[lane] + p.peer.rank, seq);
-            if (!peer_wait(p.peer, p.status, 0, seq, 3)) *abortp = 1, good = false;
+            if (!peer_wait(p.peer.flags[p.peer.rank], p.peer.rank, p.peer.world, p.peer.wait_clocks, p.status, 0, seq, 3))
+                *abortp = 1, good = false;
         }
         uint32_t s = 0, ph = 0;
         for (uint32_t j = 0; good && j < n_local; ++j) {
@@ -502,7 +515,9 @@ __global__ void __launch_bounds__(kThreads, TESSL_GEMV_MMA_MIN_BLOCKS) q4_gemv_m
                 __threadfence();  // the other blocks' stores (fenced before their tickets) precede the signal
                 if ((uint32_t)lane < p.peer.world && (uint32_t)lane != p.peer.rank)
                     st_release_sys(p.peer.flags[lane] + 8 + p.peer.rank, seq);
-                if (peer_wait(p.peer, p.status, 8, seq, 4) && lane == 0) mine[17] = 0, mine[16] = seq;
+                const bool done = p.peer.defer != 0 ||
+                                  peer_wait(mine, p.peer.rank, p.peer.world, p.peer.wait_clocks, p.status, 8, seq, 4);
+                if (done && lane == 0) mine[17] = 0, mine[16] = seq;
             }
         }
     } else {
@@ -513,6 +528,15 @@ __global__ void __launch_bounds__(kThreads, TESSL_GEMV_MMA_MIN_BLOCKS) q4_gemv_m
         const uint32_t G = 1u << p.group_shift;
         // x is written by the preceding kernel in a decode chain: wait for it.
         asm volatile("griddepcontrol.wait;" ::: "memory");
+        if (p.xwait.world > 1) {
+            // x is a gathered vector whose exchange did not wait for the peers: their slices are here once their
+            // completion flags have reached this rank's call counter (final: the exchanging kernel has finished)
+            const uint32_t seq = *(volatile const uint32_t *)(p.xwait.flags + 16);
+            if (!peer_wait(p.xwait.flags, p.xwait.rank, p.xwait.world, p.xwait.wait_clocks, p.status, 8, seq, 5)) {
+                *abortp = 1;  // the other roles leave their loops; nothing is computed from an incomplete x
+                return;
+            }
+        }
         // B fragments of the slice: word (jj, u) of this lane covers columns
         // k0 + jj G + t G / 4 + 8 u .. + 7, in the order 0,4,1,5,2,6,3,7 that the
         // nibble-pair extraction below produces.
@@ -579,7 +603,13 @@ __global__ void __launch_bounds__(kThreads, TESSL_GEMV_MMA_MIN_BLOCKS) q4_gemv_m
                 for (int win = 0; win < NWIN; ++win) {
                     const uint32_t xst = xstage + win * kXStageBytes;
                     uint4 r = make_uint4(0u, 0u, 0u, 0u);
-                    if ((uint32_t)lane < NW) r = __ldg(reinterpret_cast<const uint4 *>(xrow + win * KW + k0 + 8 * lane));
+                    // a coherent load: x may be a gather buffer that a peer GPU filled while this kernel was waiting
+                    if ((uint32_t)lane < NW) {
+                        asm volatile("ld.global.v4.u32 {%0,%1,%2,%3}, [%4];"
+                                     : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w)
+                                     : "l"(xrow + win * KW + k0 + 8 * lane)
+                                     : "memory");
+                    }
                     uint32_t amax = max(max(r.x & 0x7fffu, (r.x >> 16) & 0x7fffu), max(r.y & 0x7fffu, (r.y >> 16) & 0x7fffu));
                     amax = max(amax, max(max(r.z & 0x7fffu, (r.z >> 16) & 0x7fffu), max(r.w & 0x7fffu, (r.w >> 16) & 0x7fffu)));
 #pragma unroll

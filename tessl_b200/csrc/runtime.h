@@ -271,10 +271,13 @@ Result gemm_q4_mlx_tensorops(TesslRuntime *rt, const TesslQ4MlxBank &bank, const
                              const TesslBuf &y, const TesslQuantShape &shape, uint32_t m, OutKind out);
 Result peer_gather(TesslRuntime *rt, const TesslPeerGather &gather);
 Result gemv_q4_mlx_simd_sharded(TesslRuntime *rt, const TesslQ4MlxBank &bank, const TesslBuf &x_bf16,
-                                const TesslPeerGather &gather, const TesslQuantShape &shape, bool y_as_bf16);
+                                const TesslPeerGather &gather, const TesslQuantShape &shape, bool y_as_bf16, bool defer = false);
 Result gemv_q4_mlx_gate_up_silu_sharded(TesslRuntime *rt, const TesslQ4MlxBank &gate, const TesslQ4MlxBank &up,
                                         const TesslBuf &x_bf16, const TesslPeerGather &gather, const TesslQuantShape &shape,
-                                        bool mid_as_bf16);
+                                        bool mid_as_bf16, bool defer = false);
+Result peer_wait(TesslRuntime *rt, const TesslPeerGather &gather);
+Result gemv_q4_mlx_simd_gathered(TesslRuntime *rt, const TesslQ4MlxBank &bank, const TesslPeerGather &gather, const TesslBuf &y,
+                                 const TesslQuantShape &shape, const TesslBuf *resid, OutKind out);
 Result prefill_as_small_batches(TesslRuntime *rt, const TesslQ4MlxBank &bank, const TesslBuf &x_bf16, const TesslBuf &y,
                                 const TesslQuantShape &shape, uint32_t m, OutKind out, bool *handled);
 Result q8_mlx_mma(TesslRuntime *rt, const TesslBuf &codes, const TesslBuf &sb, const TesslBuf &x_bf16, const TesslBuf &y,

@@ -165,20 +165,37 @@ class PeerGather:
         from . import capi
         capi.call("tessl_peer_gather", rt.handle, ctypes.byref(self._desc))
 
-    def gemv(self, rt, bank, x_bf16, shape, y_as_bf16: bool = False) -> None:
+    def wait(self, rt) -> None:
+        """`tessl_peer_wait`: the wait a deferred exchange left to its reader, as a launch of its own."""
+        import ctypes
+
+        from . import capi
+        capi.call("tessl_peer_wait", rt.handle, ctypes.byref(self._desc))
+
+    def gemv_from_gathered(self, rt, bank, y, shape, resid=None, y_as_bf16: bool = False) -> None:
+        """`tessl_gemv_q4_mlx_simd_gathered`: y = W x with x the gathered vector of this descriptor; the kernel waits
+        for the peers' slices itself (what a deferred exchange leaves undone)."""
+        import ctypes
+
+        from . import capi
+        r = ctypes.byref(resid.c()) if resid is not None else None
+        capi.call("tessl_gemv_q4_mlx_simd_gathered", rt.handle, bank.c(), ctypes.byref(self._desc), y.c(), shape.c(), r,
+                  1 if y_as_bf16 else 0)
+
+    def gemv(self, rt, bank, x_bf16, shape, y_as_bf16: bool = False, defer: bool = False) -> None:
         """`tessl_gemv_q4_mlx_simd_sharded`: this rank's slice of W x computed and exchanged by one kernel;
         afterwards `full(dtype)` holds every rank's slice."""
         import ctypes
 
         from . import capi
-        capi.call("tessl_gemv_q4_mlx_simd_sharded", rt.handle, bank.c(), x_bf16.c(), ctypes.byref(self._desc), shape.c(),
-                  1 if y_as_bf16 else 0)
+        capi.call("tessl_gemv_q4_mlx_simd_sharded_deferred" if defer else "tessl_gemv_q4_mlx_simd_sharded", rt.handle,
+                  bank.c(), x_bf16.c(), ctypes.byref(self._desc), shape.c(), 1 if y_as_bf16 else 0)
 
-    def gate_up_silu(self, rt, gate, up, x_bf16, shape, mid_as_bf16: bool = True) -> None:
+    def gate_up_silu(self, rt, gate, up, x_bf16, shape, mid_as_bf16: bool = True, defer: bool = False) -> None:
         """`tessl_gemv_q4_mlx_gate_up_silu_sharded`: the fused gate/up projection on this rank's rows, exchanged
         by the same kernel."""
         import ctypes
 
         from . import capi
-        capi.call("tessl_gemv_q4_mlx_gate_up_silu_sharded", rt.handle, gate.c(), up.c(), x_bf16.c(),
-                  ctypes.byref(self._desc), shape.c(), 1 if mid_as_bf16 else 0)
+        capi.call("tessl_gemv_q4_mlx_gate_up_silu_sharded_deferred" if defer else "tessl_gemv_q4_mlx_gate_up_silu_sharded",
+                  rt.handle, gate.c(), up.c(), x_bf16.c(), ctypes.byref(self._desc), shape.c(), 1 if mid_as_bf16 else 0)

@@ -16,7 +16,7 @@ import sys
 import numpy as np
 import pytest
 
-from gpu_util import rt, upload_bank  # noqa: F401
+from gpu_util import rt, seeded_f32, upload_bank  # noqa: F401
 from tessl_b200 import capi, nn, synth
 
 pytestmark = pytest.mark.gpu
@@ -116,6 +116,57 @@ def test_a_peer_that_never_arrives_makes_the_bounded_wait_run_out(cols):
         assert np.array_equal(b.read(np.uint32, 64), np.arange(64, dtype=np.uint32))
 
 
+@pytest.mark.parametrize("cols", [4096, 1536])  # the wait inside the GEMV kernel, and as a launch of its own
+def test_a_reader_of_a_gathered_vector_whose_peer_never_finishes_gives_up(cols):
+    """The reader's side of a deferred exchange: this rank's call counter says one exchange was launched, the
+    "peer" never reports completion. The bounded wait runs out, the call reports it, the runtime is poisoned and
+    nothing was computed from the incomplete vector; a fresh runtime works."""
+    import torch
+
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    rows = 256
+    r = nn.Runtime()
+    try:
+        packed, sb = synth.q4_bank(21, rows, cols, 64)
+        bank = upload_bank(r, packed, sb)
+        bufs = [r.buffer_from(np.zeros(cols, np.uint16)) for _ in range(2)]  # world * bytes_per_rank = cols * 2 bytes
+        f0 = np.zeros(32, np.uint32)
+        f0[16] = 1  # one exchange launched by this rank; flag 8 + 1 (the peer's completion) stays 0
+        flags = [r.buffer_from(f0), r.buffer_from(np.zeros(32, np.uint32))]
+        y = seeded_f32(r, rows)
+        r.set_peer_wait_limit(2_000_000)
+        d = _desc(2, 0, cols, [b.ptr for b in bufs], [f.ptr for f in flags])
+        with pytest.raises(capi.TesslError) as e:
+            capi.call("tessl_gemv_q4_mlx_simd_gathered", r.handle, bank.c(), ctypes.byref(d), y.c(),
+                      nn.QuantShape(rows, cols, 64).c(), None, 0)
+        assert "gave up a bounded wait" in str(e.value) and "role 80" in str(e.value), str(e.value)
+        assert r.is_poisoned()
+    finally:
+        r.close()
+    with nn.Runtime() as fresh:
+        b = fresh.buffer_from(np.arange(64, dtype=np.uint32))
+        assert np.array_equal(b.read(np.uint32, 64), np.arange(64, dtype=np.uint32))
+
+
+def test_a_gathered_reader_on_one_rank_is_the_plain_operator(rt):
+    rows, cols = 264, 4096
+    packed, sb = synth.q4_bank(31, rows, cols, 64)
+    bank = upload_bank(rt, packed, sb)
+    xv = synth.normal_bf16(32, cols)
+    buf = rt.buffer_from(xv)
+    flags = rt.buffer_from(np.zeros(32, np.uint32))
+    d = _desc(1, 0, cols * 2, [buf.ptr], [flags.ptr])
+    a, b = seeded_f32(rt, rows), seeded_f32(rt, rows)
+    capi.call("tessl_gemv_q4_mlx_simd_gathered", rt.handle, bank.c(), ctypes.byref(d), a.c(), nn.QuantShape(rows, cols, 64).c(), None, 0)
+    nn.gemv_q4_mlx_simd(rt, bank, buf, b, nn.QuantShape(rows, cols, 64))
+    assert np.array_equal(a.read(np.uint32, rows), b.read(np.uint32, rows))
+    capi.call("tessl_peer_wait", rt.handle, ctypes.byref(d))  # one rank: nothing to wait for, nothing launched
+    with pytest.raises(capi.TesslError, match="gathered x"):
+        capi.call("tessl_gemv_q4_mlx_simd_gathered", rt.handle, bank.c(), ctypes.byref(_desc(1, 0, 64, [buf.ptr], [flags.ptr])),
+                  a.c(), nn.QuantShape(rows, cols, 64).c(), None, 0)
+
+
 _CHILD = r"""
 import os, sys
 import numpy as np, torch, torch.distributed as dist
@@ -175,6 +226,52 @@ for rows, cols, group, bf16 in ((12288, 4096, 64, True), (4104, 2048, 32, False)
             pg.run(rt)  # the stand-alone exchange on the same descriptor, between fused calls
             assert int(gathered().abs().max().item()) == 0
         dist.barrier()  # nobody starts the next call before everyone has compared
+
+    # deferred exchange: the producing kernel does not wait for the peers, the kernel that reads the gathered vector
+    # does (in the kernel for widths the tensor-core GEMV takes, as a launch of its own otherwise); a down-like
+    # projection over the gathered vector against the single-GPU chain, bit for bit
+    if bf16 and rows % (8 * world) == 0:
+        dp, dsb = dev_bank(300 + rows, 512, rows, 64) if rows in (1024, 2048, 4096, 8192, 12288) else (None, None)
+        if dp is not None:
+            down = as_bank(dp, dsb)
+            keep += [dp, dsb]
+            y_got = torch.empty(512, device="cuda")
+            y_want = torch.empty(512, device="cuda")
+            mid_ref = torch.empty(rows, dtype=torch.int16, device="cuda")
+            sdn = nn.QuantShape(512, rows, 64)
+            for call in range(6):
+                x = xs(900 + call + rows, cols)
+                pg.gate_up_silu(rt, loc_g, loc_u, B(x), shape_l, mid_as_bf16=True, defer=True)
+                if call % 2 == 0:
+                    pg.gemv_from_gathered(rt, down, B(y_got), sdn)
+                else:
+                    pg.wait(rt)
+                    nn.gemv_q4_mlx_simd(rt, down, nn.GpuBuffer(pg.full(torch.int16).data_ptr(), rows * 2), B(y_got), sdn)
+                nn.gemv_q4_mlx_gate_up_silu(rt, full_g, full_u, B(x), B(mid_ref), shape_f, True)
+                nn.gemv_q4_mlx_simd(rt, down, B(mid_ref), B(y_want), sdn)
+                assert torch.equal(gathered(), mid_ref), (rank, rows, "deferred mid", call)
+                assert torch.equal(y_got.view(torch.int32), y_want.view(torch.int32)), (rank, rows, "deferred down", call)
+                dist.barrier()
+            # and replayed from a graph: exchange + reader, three times per replay
+            xg2 = xs(7000, cols)
+            rt.set_encode_only(True)
+            g2 = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g2, stream=st):
+                for i in range(3):
+                    pg.gate_up_silu(rt, loc_g, loc_u, B(xg2), shape_l, mid_as_bf16=True, defer=True)
+                    pg.gemv_from_gathered(rt, down, B(y_got), sdn)
+            for rep in range(3):
+                with torch.cuda.stream(st):
+                    xg2.copy_(xs(7100 + rep, cols))
+                    g2.replay()
+                rt.synchronize()
+                rt.set_encode_only(False)
+                nn.gemv_q4_mlx_gate_up_silu(rt, full_g, full_u, B(xg2), B(mid_ref), shape_f, True)
+                nn.gemv_q4_mlx_simd(rt, down, B(mid_ref), B(y_want), sdn)
+                assert torch.equal(y_got.view(torch.int32), y_want.view(torch.int32)), (rank, rows, "deferred graph", rep)
+                rt.set_encode_only(True)
+                dist.barrier()
+            rt.set_encode_only(False)
 
     # replayed from a CUDA graph: four calls per replay, the activations rewritten between replays
     xg = xs(999, cols)
