@@ -9,8 +9,13 @@
 //      buffer have finished: they precede the peer's gather in stream order) and
 //      waits for every peer's arrival,
 //   2. stores its slice into every peer's buffer (plain 16-byte peer stores),
-//   3. fences at system scope, tells every peer its slice is complete and waits
-//      for every peer's completion.
+//   3. tells every peer its slice is complete and waits for every peer's
+//      completion. A system-scope fence (or an acquire or release at that scope)
+//      costs ~1.8 us here, so there is exactly one per launch: every block
+//      orders its stores before its ticket at device scope, and the block that
+//      draws the last ticket fences once at system scope (cumulative over the
+//      tickets it observed) before a relaxed store of the flag. Polls are
+//      relaxed too: what they announce is read by later kernels of the stream.
 // Flags are monotonically increasing call numbers kept in peer-mapped memory
 // (`flags` of rank r: [0, 8) arrivals by source rank, [8, 16) completions by
 // source rank, [16] this rank's own call counter, [17] a ticket counter of the
@@ -35,14 +40,14 @@ struct PeerGatherParams {
     uint32_t *status;
 };
 
-__device__ __forceinline__ void st_release_sys(uint32_t *p, uint32_t v)
+__device__ __forceinline__ void st_relaxed_sys(uint32_t *p, uint32_t v)
 {
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+    asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
-__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t *p)
+__device__ __forceinline__ uint32_t ld_relaxed_sys(const uint32_t *p)
 {
     uint32_t v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
     return v;
 }
 
@@ -53,7 +58,7 @@ __device__ __forceinline__ bool wait_peers(const PeerGatherParams &p, uint32_t b
     if (threadIdx.x < p.world && threadIdx.x != p.rank) {
         const uint32_t *f = p.flags[p.rank] + base + threadIdx.x;
         const long long t0 = clock64();
-        while ((int32_t)(ld_acquire_sys(f) - seq) < 0) {
+        while ((int32_t)(ld_relaxed_sys(f) - seq) < 0) {
             if (clock64() - t0 > p.wait_clocks) {
                 *(volatile uint32_t *)p.status = (0x50u << 24) | (code << 16) | threadIdx.x;
                 ok_ = false;
@@ -79,7 +84,7 @@ __global__ void __launch_bounds__(1024, 1) peer_gather_kernel(const PeerGatherPa
     const uint32_t seq = *(volatile uint32_t *)(mine + 16) + 1;
     // 1. arrival: block 0 tells the peers, every block waits for theirs
     if (blockIdx.x == 0 && threadIdx.x < p.world && threadIdx.x != p.rank)
-        st_release_sys(p.flags[threadIdx.x] + p.rank, seq);
+        st_relaxed_sys(p.flags[threadIdx.x] + p.rank, seq);  // announces no data of this kernel
     if (!wait_peers(p, 0, seq, 1)) return;
     // 2. this rank's slice into every peer's buffer, the blocks sharing the 16-byte pieces
     const uint64_t n16 = p.bytes_per_rank / 16;
@@ -89,15 +94,18 @@ __global__ void __launch_bounds__(1024, 1) peer_gather_kernel(const PeerGatherPa
         for (uint32_t r = 0; r < p.world; ++r)
             if (r != p.rank) reinterpret_cast<uint4 *>(p.buf[r] + (size_t)p.rank * p.bytes_per_rank)[i] = v;
     }
-    __threadfence_system();
+    __threadfence();
     __syncthreads();
     // 3. completion, by the last block to get here
     __shared__ uint32_t ticket;
     if (threadIdx.x == 0) ticket = atomicAdd(mine + 17, 1u);
     __syncthreads();
     if (ticket != gridDim.x - 1) return;
-    __threadfence();  // the other blocks' stores (fenced at system scope before their tickets) precede the signal
-    if (threadIdx.x < p.world && threadIdx.x != p.rank) st_release_sys(p.flags[threadIdx.x] + 8 + p.rank, seq);
+    // every block's stores precede its ticket at device scope, all tickets were observed here: this one fence
+    // puts them all before the flag at system scope
+    if (threadIdx.x < 32) __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x < p.world && threadIdx.x != p.rank) st_relaxed_sys(p.flags[threadIdx.x] + 8 + p.rank, seq);
     if (!wait_peers(p, 8, seq, 2)) return;
     if (threadIdx.x == 0) mine[17] = 0, mine[16] = seq;
 }
@@ -111,7 +119,7 @@ __global__ void peer_wait_kernel(const uint32_t *mine, uint32_t rank, uint32_t w
     const uint32_t seq = *(volatile const uint32_t *)(mine + 16);
     if (threadIdx.x < world && threadIdx.x != rank) {
         const long long t0 = clock64();
-        while ((int32_t)(ld_acquire_sys(mine + 8 + threadIdx.x) - seq) < 0) {
+        while ((int32_t)(ld_relaxed_sys(mine + 8 + threadIdx.x) - seq) < 0) {
             if (clock64() - t0 > wait_clocks) {
                 *(volatile uint32_t *)status = (0x50u << 24) | (5u << 16) | threadIdx.x;
                 break;

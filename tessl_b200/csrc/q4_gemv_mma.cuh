@@ -520,6 +520,7 @@ __global__ void __launch_bounds__(kThreads, TESSL_GEMV_MMA_MIN_BLOCKS) q4_gemv_m
             uint32_t ticket = 0;
             if (lane == 0) ticket = atomicAdd(mine + 17, 1u);
             ticket = __shfl_sync(0xffffffffu, ticket, 0);
+            __syncwarp();  // lane 0's observation of the tickets, ordered before the other lanes' fences and stores
             if (ticket == gridDim.x - 1) {
                 __threadfence_system();
                 if ((uint32_t)lane < p.peer.world && (uint32_t)lane != p.peer.rank)
