@@ -347,8 +347,9 @@ Result launch_mma_one(TesslRuntime *rt, const Q4GemvParams &p, int m, const MmaW
     TESSL_TRY(smem_opt_in(rt, reinterpret_cast<const void *>(kernel), smem, "q4_gemv_mma: shared memory opt-in", true));
     const uint32_t grid = std::min<uint32_t>(rb, (uint32_t)rt->sm_count);
     // four rows per bulk copy wherever two row pairs are adjacent in memory (one bank, dense rows): 151936 x 4096
-    // 58.8 -> 52.7 us, 6144 x 4096 5.30 -> 5.05 us, 12288 x 4096 8.00 -> 7.90 us on one box, back to back
-    mp.quads = (!BATCH && NWIN == 1 && w.row_pitch == 0 && !p.staged) ? 1u : 0u;
+    // 58.8 -> 52.7 us, 6144 x 4096 5.30 -> 5.05 us, 12288 x 4096 8.00 -> 7.90 us on one box, back to back.
+    // Not for Q8: its row pair is already 8 KB, and 16 KB copies ran 14336 x 4096 in 17.0 us against 14.5.
+    mp.quads = (!BATCH && !Q8 && NWIN == 1 && w.row_pitch == 0 && !p.staged) ? 1u : 0u;
     cudaLaunchConfig_t lc{};
     lc.gridDim = dim3(grid), lc.blockDim = dim3(q4m::kThreads), lc.dynamicSmemBytes = smem;
     lc.stream = rt->stream;
@@ -453,6 +454,18 @@ Result launch_mma_q8_sw(TesslRuntime *rt, const Q4GemvParams &p, int m)
     // 4096 codes per row: a 16-row stage with the batch's partial sums is 77 KB and only two fit; 8-row stages
     // (half of each MMA idle, which this format can afford: one MMA per 8 bytes of weights) give five.
     if (SW == 16 && m > 1) return launch_mma_one<SW, WPG, 1, true, true, 1, 8>(rt, p, m);
+    if (SW == 16 && m == 1) {
+        // One row of x over 4096 codes per row is bound by the stream, not by the consumers (a stage's compute does
+        // not depend on its height, its bytes do), so the stage height that leaves the shortest tail wins: the
+        // busiest SM streams ceil(stages / SMs) x height rows. 14336 rows: 16 -> 14.4 us, 12 -> 14.05, 10 -> 13.7,
+        // 8 -> 15.4 (half of every MMA idle begins to cost). Ties go to the taller stage.
+        uint32_t rows = 0;
+        for (int s = 0; s < p.nseg; ++s) rows += p.seg[s].rows;
+        const uint32_t sms = (uint32_t)rt->sm_count;
+        auto tail = [&](uint32_t h) { return (((rows + h - 1) / h + sms - 1) / sms) * h; };
+        if (tail(10) < tail(16) && tail(10) < tail(12)) return launch_mma_one<SW, WPG, 1, false, true, 1, 10>(rt, p, m);
+        if (tail(12) < tail(16)) return launch_mma_one<SW, WPG, 1, false, true, 1, 12>(rt, p, m);
+    }
     if (m == 1) return launch_mma_one<SW, WPG, 1, false, true>(rt, p, m);
     return launch_mma_one<SW, WPG, 1, true, true>(rt, p, m);
 }
