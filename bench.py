@@ -567,11 +567,12 @@ def check_parity(torch, dist, nn, rt, L0, cpu_inputs, step, bufs, mid_full, worl
 
 
 def measure_sharded_lm_head(ctx, args, world, rank):
-    """N > 1 only: the LM head (151936 x 4096, Q4 g64), rows sharded over the ranks; every rank streams its
-    slice and the GEMV kernel itself stores the bf16 logits into all ranks' gather buffers (NCCL all-gather
-    on the fallback). Device time of the slowest rank, whole-job weight bytes per second. The launches rotate
-    over enough different slices that the stream exceeds L2 at every N; the first slice's gathered logits are
-    compared on every rank, bit for bit, with the single-GPU operator on the unsharded bank."""
+    """N > 1 only: the LM head (151936 x 4096, Q4 g64) at M = 1 and M = 8, rows sharded over the ranks; every
+    rank streams its slice; at M = 1 the GEMV kernel itself stores the bf16 logits into all ranks' gather
+    buffers, at M = 8 the stand-alone exchange follows the small-batch GEMM (NCCL all-gather on the fallback).
+    Device time of the slowest rank, whole-job weight bytes per second. The launches rotate over enough
+    different slices that the stream exceeds L2 at every N; the first slice's gathered logits are compared on
+    every rank, bit for bit, with the single-GPU operator on the unsharded bank (a mismatch ends the run)."""
     torch, dist, nn, rt, st = ctx["torch"], ctx["dist"], ctx["nn"], ctx["rt"], ctx["st"]
     from tessl_b200 import sharded
     rows, cols = 151936, HIDDEN
@@ -592,85 +593,118 @@ def measure_sharded_lm_head(ctx, args, world, rank):
             keep += [packed, sb]
             full0 = nn.Q4MlxBank(B(packed), B(sb))
         del packed, sb
-    x = ctx["bufs"]["x_mlp"]
-    peer = None
-    if ctx.get("gather", "nccl") != "nccl":
-        try:
-            peer = sharded.PeerGather(-(-per * 2 // 16) * 16)
-        except Exception:  # noqa: BLE001
-            peer = None
-        agreed = torch.tensor([1 if peer is not None else 0], device=ctx["dev"])
-        dist.all_reduce(agreed, op=dist.ReduceOp.MIN)  # all ranks take the same exchange
-        if int(agreed.item()) == 0:
-            peer = None
-    if peer is not None:
-        y_full = peer.full(torch.bfloat16)
-        slot = peer.bytes_per_rank // 2
-    else:
-        y_local = torch.zeros(per, device=ctx["dev"], dtype=torch.bfloat16)
-        y_full = torch.empty(per * world, device=ctx["dev"], dtype=torch.bfloat16)
-        yl_b = B(y_local)
-        slot = per
+    x1 = ctx["bufs"]["x_mlp"]
+    use_peer = ctx.get("gather", "nccl") != "nccl"
     shape = nn.QuantShape(sh.local_rows, cols, GROUP)
-    # many calls per replay: the ranks leave the barrier before a replay tens of microseconds apart, and the
-    # first call of a replay waits for the last rank to arrive
-    iters = 16 * nslices
-
-    def call(i):
-        if peer is not None:
-            peer.gemv(rt, banks[i % nslices], x, shape, y_as_bf16=True)
-        else:
-            nn.gemv_q4_mlx_simd(rt, banks[i % nslices], x, yl_b, shape, y_as_bf16=True)
-            with torch.cuda.stream(st):
-                dist.all_gather_into_tensor(y_full, y_local)
-
-    # parity first: slice 0 against the unsharded bank
-    call(0)
-    rt.synchronize()
-    torch.cuda.synchronize()
-    want = torch.empty(rows, device=ctx["dev"], dtype=torch.bfloat16)
-    nn.gemv_q4_mlx_simd(rt, full0, x, B(want), nn.QuantShape(rows, cols, GROUP), y_as_bf16=True)
-    got = torch.cat([y_full.view(world, slot)[r, : sharded.make_shard(rows, world, r).local_rows] for r in range(world)])
-    t = torch.tensor([1 if torch.equal(got.view(torch.int16), want.view(torch.int16)) else 0], device=ctx["dev"])
-    dist.all_reduce(t, op=dist.ReduceOp.MIN)
-    parity = "ok" if int(t.item()) == 1 else "MISMATCH"
-    if parity != "ok":
-        raise SystemExit(f"bench: rank {rank}: sharded LM-head logits differ from the single-GPU operator")
-    del full0, want
-
-    rt.set_encode_only(True)
-    for i in range(3):
-        call(i)
-    rt.synchronize()
-    torch.cuda.synchronize()
-    dist.barrier()
-    g = torch.cuda.CUDAGraph()
-    with torch.cuda.graph(g, stream=st):
-        for i in range(iters):
-            call(i)
-    best = 1e30
-    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    for rep in range(4):
-        dist.barrier()
-        with torch.cuda.stream(st):
-            a.record(st)
-            g.replay()
-            b.record(st)
-        b.synchronize()
-        if rep:
-            best = min(best, a.elapsed_time(b) / iters)
-    rt.set_encode_only(False)
-    t = torch.tensor([best], device=ctx["dev"])
-    dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    us = float(t.item()) * 1e3
     nbytes = q4_weight_bytes(rows, cols)
-    return {"us": round(us, 2), "weight_gbs": round(nbytes / us / 1e3, 1), "rows_per_gpu": int(sh.local_rows),
-            "slices_in_rotation": nslices, "rotation_mb_per_gpu": round(nslices * slice_bytes / 1e6, 1),
-            "parity_n": parity,
-            "how": "one launch per call: GEMV on this rank's row slice" + (
+    out = {}
+    for m in (1, 8):
+        # m = 1: the exchanging GEMV (one launch). m = 8: the small-batch GEMM on the slice, its [8, rows / N] bf16
+        # block written into this rank's part of the gather buffer, then the stand-alone exchange (two launches).
+        peer = None
+        if use_peer:
+            try:
+                peer = sharded.PeerGather(-(-per * m * 2 // 16) * 16)
+            except Exception:  # noqa: BLE001
+                peer = None
+            agreed = torch.tensor([1 if peer is not None else 0], device=ctx["dev"])
+            dist.all_reduce(agreed, op=dist.ReduceOp.MIN)  # all ranks take the same exchange
+            if int(agreed.item()) == 0:
+                peer = None
+        if m == 1:
+            x, xb = None, x1
+        else:
+            xgen = torch.Generator(device="cuda")
+            xgen.manual_seed(0x7E55AB)
+            x = torch.randn(m * cols, device=ctx["dev"], generator=xgen).to(torch.bfloat16)
+            xb = B(x)
+        if peer is not None:
+            y_full = peer.full(torch.bfloat16)
+            slot = peer.bytes_per_rank // 2
+            yl_b = B(peer.local(torch.bfloat16))
+        else:
+            y_local = torch.zeros(per * m, device=ctx["dev"], dtype=torch.bfloat16)
+            y_full = torch.empty(per * m * world, device=ctx["dev"], dtype=torch.bfloat16)
+            yl_b = B(y_local)
+            slot = per * m
+        # many calls per replay: the ranks leave the barrier before a replay tens of microseconds apart, and the
+        # first call of a replay waits for the last rank to arrive
+        iters = (16 if m == 1 else 8) * nslices
+
+        def call(i):
+            bank = banks[i % nslices]
+            if m == 1 and peer is not None:
+                peer.gemv(rt, bank, xb, shape, y_as_bf16=True)
+                return
+            if m == 1:
+                nn.gemv_q4_mlx_simd(rt, bank, xb, yl_b, shape, y_as_bf16=True)
+            else:
+                nn.gemm_q4_mlx(rt, bank, xb, yl_b, shape, m, y_as_bf16=True)
+            if peer is not None:
+                peer.run(rt)
+            else:
+                with torch.cuda.stream(st):
+                    dist.all_gather_into_tensor(y_full, y_local)
+
+        # parity first: slice 0 against the unsharded bank
+        call(0)
+        rt.synchronize()
+        torch.cuda.synchronize()
+        want = torch.empty(m * rows, device=ctx["dev"], dtype=torch.bfloat16)
+        if m == 1:
+            nn.gemv_q4_mlx_simd(rt, full0, xb, B(want), nn.QuantShape(rows, cols, GROUP), y_as_bf16=True)
+        else:
+            nn.gemm_q4_mlx(rt, full0, xb, B(want), nn.QuantShape(rows, cols, GROUP), m, y_as_bf16=True)
+        # rank r's block is [m, its rows]: the gathered result is the single-GPU [m, rows] cut by columns
+        got = torch.cat([y_full.view(world, slot)[r, : m * lr].view(m, lr)
+                         for r in range(world) for lr in [sharded.make_shard(rows, world, r).local_rows]], dim=1)
+        t = torch.tensor([1 if torch.equal(got.reshape(-1).view(torch.int16), want.view(torch.int16)) else 0],
+                         device=ctx["dev"])
+        dist.all_reduce(t, op=dist.ReduceOp.MIN)
+        if int(t.item()) != 1:
+            raise SystemExit(f"bench: rank {rank}: sharded LM-head logits (m = {m}) differ from the single-GPU operator")
+        del want
+
+        rt.set_encode_only(True)
+        for i in range(3):
+            call(i)
+        rt.synchronize()
+        torch.cuda.synchronize()
+        dist.barrier()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=st):
+            for i in range(iters):
+                call(i)
+        best = 1e30
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        for rep in range(4):
+            dist.barrier()
+            with torch.cuda.stream(st):
+                a.record(st)
+                g.replay()
+                b.record(st)
+            b.synchronize()
+            if rep:
+                best = min(best, a.elapsed_time(b) / iters)
+        rt.set_encode_only(False)
+        t = torch.tensor([best], device=ctx["dev"])
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        us = float(t.item()) * 1e3
+        if m == 1:
+            how = "one launch per call: GEMV on this rank's row slice" + (
                 ", its reducer warps storing the bf16 logits into every rank's gather buffer over NVLink, one flag "
                 "exchange at the end" if peer is not None else " + one NCCL all-gather of the bf16 logits")
-                   + "; all calls in one CUDA graph"}, parity
+        else:
+            how = "two launches per call: the small-batch GEMM on this rank's row slice, then " + (
+                "the stand-alone peer-memory exchange of its [8, rows / N] bf16 block" if peer is not None
+                else "one NCCL all-gather of its [8, rows / N] bf16 block")
+        out[f"lm_head 151936x4096 m={m} sharded over {world} GPUs"] = {
+            "us": round(us, 2), "weight_gbs": round(nbytes / us / 1e3, 1), "rows_per_gpu": int(sh.local_rows),
+            "slices_in_rotation": nslices, "rotation_mb_per_gpu": round(nslices * slice_bytes / 1e6, 1),
+            "parity_n": "ok", "how": how + "; all calls in one CUDA graph"}
+        del g, peer, y_full
+        torch.cuda.empty_cache()
+    return out, "ok"
 
 
 def measure_e2e_python(ctx, args):
@@ -1026,7 +1060,7 @@ def main():
             e2e["how"] += f"; on each of the {world} ranks, slowest rank's time"
             line["e2e"] = e2e
             sharded_head, head_parity = measure_sharded_lm_head(ctx, args, world, rank)
-            line["extra"] = {f"lm_head 151936x4096 m=1 sharded over {world} GPUs": sharded_head}
+            line["extra"] = sharded_head
             if head_parity != "ok":
                 line["parity_n"] = head_parity
         except Exception as e:  # noqa: BLE001
