@@ -339,7 +339,8 @@ Result launch_mma_one(TesslRuntime *rt, const Q4GemvParams &p, int m, const MmaW
     const uint32_t gpr = p.cols >> p.group_shift;
     const uint32_t part = BATCH ? q4m::kConsumers * 16 * 8 * 4 : q4m::kConsumers * 16 * 4;
     const uint32_t stage_bytes = ROWS * ((p.cols >> 1) + q4m::kRowPad) + ROWS * gpr * 4 + part;
-    const uint32_t x_stage = 16 + q4m::kConsumers * q4m::kXStageBytes * NWIN;  // the warps' staged slices of x (M = 1)
+    // the warps' staged slices of x: only the Q4 kernel for one row of x stages them
+    const uint32_t x_stage = 16 + ((BATCH || Q8) ? 0u : q4m::kConsumers * q4m::kXStageBytes * NWIN);
     uint32_t stages = std::min<uint32_t>(8u, (kMmaSmemBudget - x_stage) / (stage_bytes + 24));
     if (stages < 2) return "q4_gemv_mma: the ring does not fit two stages";
     mp.stages = stages;
