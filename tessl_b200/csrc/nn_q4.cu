@@ -316,7 +316,6 @@ Result launch_mma_one(TesslRuntime *rt, const Q4GemvParams &p, int m, const MmaW
     mp.sb_pitch = w.sb_pitch ? w.sb_pitch : (p.cols >> p.group_shift) * 4;
     mp.x_pitch = w.x_pitch ? w.x_pitch : (Q8 ? p.cols >> 1 : p.cols);
     mp.status = rt->status_dev;
-    mp.staged = STAGED ? 1u : 0u;
     if ((p.staged != 0) != STAGED) return "q4_gemv: the staged layout runs on the one-row Q4 kernel only";
     if (p.peer) {
         const TesslPeerGather &g = *static_cast<const TesslPeerGather *>(p.peer);
@@ -325,7 +324,7 @@ Result launch_mma_one(TesslRuntime *rt, const Q4GemvParams &p, int m, const MmaW
             mp.peer.out[r] = static_cast<uint8_t *>(g.buffers[r]) + (size_t)g.rank * g.bytes_per_rank;
             mp.peer.flags[r] = g.flags[r];
         }
-        mp.peer.rank = g.rank, mp.peer.world = g.world;
+        mp.peer.rank = g.rank, mp.peer.world = g.world, mp.peer_world = g.world;
         mp.peer.wait_clocks = rt->peer_wait_clocks ? (long long)rt->peer_wait_clocks : kPeerWaitClocks;
         mp.peer.defer = p.peer_defer ? 1u : 0u;
     }
@@ -333,20 +332,24 @@ Result launch_mma_one(TesslRuntime *rt, const Q4GemvParams &p, int m, const MmaW
         const TesslPeerGather &g = *static_cast<const TesslPeerGather *>(p.xwait);
         if (BATCH || Q8) return "q4_gemv: a gathered x is one row";
         mp.xwait.flags = g.flags[g.rank];
-        mp.xwait.rank = g.rank, mp.xwait.world = g.world;
+        mp.xwait.rank = g.rank, mp.xwait.world = g.world, mp.xwait_world = g.world;
         mp.xwait.wait_clocks = rt->peer_wait_clocks ? (long long)rt->peer_wait_clocks : kPeerWaitClocks;
     }
     const uint32_t gpr = p.cols >> p.group_shift;
     const uint32_t part = BATCH ? q4m::kConsumers * 16 * 8 * 4 : q4m::kConsumers * 16 * 4;
     const uint32_t stage_bytes = ROWS * ((p.cols >> 1) + q4m::kRowPad) + ROWS * gpr * 4 + part;
     // the warps' staged slices of x: only the Q4 kernel for one row of x stages them
-    const uint32_t x_stage = 16 + ((BATCH || Q8) ? 0u : q4m::kConsumers * q4m::kXStageBytes * NWIN);
+    const uint32_t x_stage = 32 + ((BATCH || Q8) ? 0u : q4m::kConsumers * q4m::kXStageBytes * NWIN);
     uint32_t stages = std::min<uint32_t>(8u, (kMmaSmemBudget - x_stage) / (stage_bytes + 24));
     if (stages < 2) return "q4_gemv_mma: the ring does not fit two stages";
     mp.stages = stages;
     const size_t smem = (size_t)stages * (stage_bytes + 24) + x_stage;
     TESSL_TRY(smem_opt_in(rt, reinterpret_cast<const void *>(kernel), smem, "q4_gemv_mma: shared memory opt-in", true));
     const uint32_t grid = std::min<uint32_t>(rb, (uint32_t)rt->sm_count);
+    {
+        const uint64_t step = (((uint64_t)rb << 32) + grid - 1) / grid;  // rb <= 2^32 - 1 and grid <= rb: step fits 64 bits
+        mp.rb_step_lo = (uint32_t)step, mp.rb_step_hi = (uint32_t)(step >> 32);
+    }
     // four rows per bulk copy wherever two row pairs are adjacent in memory (one bank, dense rows): 151936 x 4096
     // 58.8 -> 52.7 us, 6144 x 4096 5.30 -> 5.05 us, 12288 x 4096 8.00 -> 7.90 us on one box, back to back.
     // Not for Q8: its row pair is already 8 KB, and 16 KB copies ran 14336 x 4096 in 17.0 us against 14.5.

@@ -37,6 +37,7 @@
 //
 // Every mbarrier wait is bounded (see q4_gemv_tma.cuh).
 #pragma once
+#include <cstddef>
 
 #include "q4_gemv_tma.cuh"
 
@@ -61,6 +62,7 @@ using q4k::smem_u32;
 #endif
 constexpr int kConsumers = 16;
 constexpr int kThreads = (kConsumers + 2) * 32;
+constexpr uint32_t kHoldFrom = 3, kHoldMaxStages = 16;  // see the producer loop
 constexpr uint32_t kRowPad = 32;  // bytes; row pitch = K / 2 + 32
 constexpr uint32_t kXStageBytes = 512 + 32;  // a warp's staged slice of x: B fragments and up to 8 group sums
 
@@ -96,15 +98,17 @@ struct XWait {
     long long wait_clocks;
 };
 
+/// Field order: what a launch without an exchange reads before its first copy and its first MMA sits in the first
+/// two 64-byte lines of the parameter block (the constant cache is cold for every launch); worth 0.02-0.04 us per
+/// launch when measured, so a tidiness more than an optimisation.
 struct Params {
-    Seg seg[3];
-    int nseg;
-    uint32_t total_rb;
-    const uint16_t *x;  // bf16 [m, cols]
-    uint32_t m;
+    // --- line 0: the scalars every role reads
     uint32_t cols;
     uint32_t group_shift;
     uint32_t stages;
+    uint32_t total_rb;
+    int nseg;
+    uint32_t m;
     int epi;
     int out_bf16;
     // A launch may cover a window of `cols` columns of longer rows (a K chunk): bytes between packed
@@ -114,14 +118,21 @@ struct Params {
     uint32_t sb_pitch;
     uint32_t x_pitch;
     uint32_t quads;  // fetch four rows per bulk copy (long streams, one bank, one row of x)
-    // The banks are in the staged layout (tessl_q4_mlx_repack_staged): units of 8 rows already in this kernel's
-    // shared-memory form - four row pairs with their pads, then the rows' scale/bias pairs - so a stage is two
-    // bulk copies.
-    uint32_t staged;
+    // Row blocks per thread block as a 32.32 fixed-point number, rounded up: block b takes the row blocks
+    // [b step >> 32, (b + 1) step >> 32) clipped to total_rb. (The division total_rb b / blocks in the kernel is a
+    // 64-bit one, executed by all eighteen warps at once: ~900 issue cycles before the block's first copy.)
+    uint32_t rb_step_lo, rb_step_hi;
+    uint32_t peer_world;   // == peer.world
+    uint32_t xwait_world;  // == xwait.world
+    // --- line 1: the activations and the first bank
+    const uint16_t *x;  // bf16 [m, cols]
+    Seg seg[3];
+    // --- cold: failure reports and the exchange
     uint32_t *status;
     Peer peer;
     XWait xwait;
 };
+static_assert(offsetof(Params, x) == 64 && offsetof(Params, seg) == 72 && sizeof(Seg) == 56, "parameter lines");
 
 // A system-scope fence, and every acquire or release at system scope, costs ~1.8 us on this GPU (measured: the
 // same for local and for peer stores). The exchange therefore polls and signals with RELAXED system-scope
@@ -237,18 +248,32 @@ __global__ void __launch_bounds__(kThreads, TESSL_GEMV_MMA_MIN_BLOCKS) q4_gemv_m
     auto done = [&](uint32_t s) { return bars + 8 * (2 * S + s); };
     // M = 1: each warp stages its slice of x once (512 bytes of B fragments + the group sums) and the
     // lanes read their fragments back, instead of every lane converting the 64 values it holds.
-    const uint32_t xstage = ((bars + 24 * S + 15u) & ~15u) + (uint32_t)warp * (kXStageBytes * NWIN);
+    const uint32_t xbar = bars + 24 * S;  // consumers: x is in registers (the producer holds the ring's tail for it)
+    const uint32_t xstage = ((bars + 24 * S + 8 + 15u) & ~15u) + (uint32_t)warp * (kXStageBytes * NWIN);
 
-    const uint32_t rb_lo = (uint32_t)((uint64_t)p.total_rb * blockIdx.x / gridDim.x);
-    const uint32_t rb_hi = (uint32_t)((uint64_t)p.total_rb * (blockIdx.x + 1) / gridDim.x);
-    const uint32_t n_local = rb_hi - rb_lo;
+    auto rb_at = [&](uint32_t b) {
+        const uint32_t v = __umulhi(b, p.rb_step_lo) + b * p.rb_step_hi;
+        return min(v, p.total_rb);
+    };
+    const uint32_t rb_lo = rb_at(blockIdx.x);
+    const uint32_t n_local = rb_at(blockIdx.x + 1) - rb_lo;
 
-    if (threadIdx.x == 0) {
-        abort_flag = 0;
-        for (uint32_t s = 0; s < S; ++s) mbar_init(full(s), 1), mbar_init(empty(s), 1), mbar_init(done(s), kConsumers);
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    // The producer warp sets up the barriers and goes straight on to its first copies: it only ARRIVES at the
+    // block's start barrier, the other warps wait there for that arrival. (With a __syncthreads() here the first
+    // copy left 2600 cycles after the block's first instruction.)
+    if (warp == kConsumers) {
+        if (lane == 0) {
+            abort_flag = 0;
+            for (uint32_t s = 0; s < S; ++s) mbar_init(full(s), 1), mbar_init(empty(s), 1), mbar_init(done(s), kConsumers);
+            mbar_init(xbar, kConsumers);
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the copies' completions see the barriers
+        }
+        __syncwarp();
+        asm volatile("bar.arrive 2, %0;" ::"n"(kThreads) : "memory");
+    } else {
+        asm volatile("bar.sync 2, %0;" ::"n"(kThreads) : "memory");
     }
-    __syncthreads();
     volatile int *abortp = &abort_flag;
     auto fail = [&](uint32_t role, uint32_t where) {
         *abortp = 1;
@@ -313,6 +338,15 @@ __global__ void __launch_bounds__(kThreads, TESSL_GEMV_MMA_MIN_BLOCKS) q4_gemv_m
                 if (lane == 0) fail(1, j);
                 break;
             }
+            // A short launch asks for three stages at once and for the rest of its ring once the consumers hold x:
+            // every block's whole ring requested at the block's start put the first stage of a block that starts late
+            // (its SM was the last to finish the previous launch) behind the other blocks' later stages, and the
+            // launch's first MMA waits for that stage. 12288 x 4096 back to back: 7.9 -> 7.2 us, 18992 x 4096 10.0 ->
+            // 9.6 us; a long stream loses the idle start instead (151936 x 4096: 52.4 -> 52.8 us), hence the limit.
+            if (j == kHoldFrom && n_local <= kHoldMaxStages && !mbar_wait(xbar, 0, abortp, 64)) {
+                if (lane == 0) fail(1, j);
+                break;
+            }
             const uint32_t nrows = min((uint32_t)RPB, seg_rows - row0);
             const uint32_t st = ring + s * stage_bytes;
             if constexpr (STAGED) {
@@ -368,7 +402,7 @@ __global__ void __launch_bounds__(kThreads, TESSL_GEMV_MMA_MIN_BLOCKS) q4_gemv_m
         // stream order, so "I am here" tells the peers they may overwrite it - then the stores as rows
         // finish, then one completion handshake by the block that finishes last. The arrival round trip
         // hides behind the weight stream; only the completion one is exposed.
-        const bool peered = !BATCH && p.peer.world > 1;
+        const bool peered = !BATCH && p.peer_world > 1;
         uint32_t seq = 0;
         bool good = true;
         if (peered) {
@@ -538,7 +572,7 @@ __global__ void __launch_bounds__(kThreads, TESSL_GEMV_MMA_MIN_BLOCKS) q4_gemv_m
         const uint32_t G = 1u << p.group_shift;
         // x is written by the preceding kernel in a decode chain: wait for it.
         asm volatile("griddepcontrol.wait;" ::: "memory");
-        if (p.xwait.world > 1) {
+        if (p.xwait_world > 1) {
             // x is a gathered vector whose exchange did not wait for the peers: their slices are here once their
             // completion flags have reached this rank's call counter (final: the exchanging kernel has finished)
             // One warp polls and pays the system-scope acquire (hidden behind the weight prefetch; taken by every
@@ -694,6 +728,7 @@ __global__ void __launch_bounds__(kThreads, TESSL_GEMV_MMA_MIN_BLOCKS) q4_gemv_m
                 xs1[jj] = __shfl_sync(0xffffffffu, xs[jj], (2 * t + 1) * 4);
             }
         }
+        if (lane == 0) mbar_arrive(xbar);  // this warp holds its x fragments: the producer may fill the rest of the ring
         const uint32_t w_off = (k0 >> 1) + t * (G / 8);  // byte offset of the lane's first word within a row
         const uint32_t sb_off = (k0 >> p.group_shift) * 4;
 
