@@ -262,13 +262,11 @@ __global__ void __launch_bounds__(kThreads, TESSL_GEMV_MMA_MIN_BLOCKS) q4_gemv_m
     // block's start barrier, the other warps wait there for that arrival. (With a __syncthreads() here the first
     // copy left 2600 cycles after the block's first instruction.)
     if (warp == kConsumers) {
-        if (lane == 0) {
-            abort_flag = 0;
-            for (uint32_t s = 0; s < S; ++s) mbar_init(full(s), 1), mbar_init(empty(s), 1), mbar_init(done(s), kConsumers);
-            mbar_init(xbar, kConsumers);
-            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the copies' completions see the barriers
-        }
+        // one barrier per lane: full and empty (one arrival each), then done and xbar (one per consumer warp)
+        if (lane == 0) abort_flag = 0;
+        if ((uint32_t)lane <= 3 * S) mbar_init(bars + 8 * lane, (uint32_t)lane < 2 * S ? 1u : (uint32_t)kConsumers);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // the copies' completions see the barriers (0.02 us)
         __syncwarp();
         asm volatile("bar.arrive 2, %0;" ::"n"(kThreads) : "memory");
     } else {
