@@ -341,6 +341,8 @@ __global__ void __launch_bounds__(kThreads, TESSL_GEMV_MMA_MIN_BLOCKS) q4_gemv_m
             // (its SM was the last to finish the previous launch) behind the other blocks' later stages, and the
             // launch's first MMA waits for that stage. 12288 x 4096 back to back: 7.9 -> 7.2 us, 18992 x 4096 10.0 ->
             // 9.6 us; a long stream loses the idle start instead (151936 x 4096: 52.4 -> 52.8 us), hence the limit.
+            // Releasing the tail earlier (at the dependency wait's return, or once x is in registers) gave 7.2 us where
+            // this gives 6.8; letting the blocks with the most stages skip the hold changed nothing.
             if (j == kHoldFrom && n_local <= kHoldMaxStages && !mbar_wait(xbar, 0, abortp, 64)) {
                 if (lane == 0) fail(1, j);
                 break;
@@ -661,8 +663,7 @@ __global__ void __launch_bounds__(kThreads, TESSL_GEMV_MMA_MIN_BLOCKS) q4_gemv_m
                     }
                     uint32_t amax = max(max(r.x & 0x7fffu, (r.x >> 16) & 0x7fffu), max(r.y & 0x7fffu, (r.y >> 16) & 0x7fffu));
                     amax = max(amax, max(max(r.z & 0x7fffu, (r.z >> 16) & 0x7fffu), max(r.w & 0x7fffu, (r.w >> 16) & 0x7fffu)));
-#pragma unroll
-                    for (int o = 16; o > 0; o >>= 1) amax = max(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+                    amax = __reduce_max_sync(0xffffffffu, amax);  // one instruction: this chain is the launch's start-up path
                     e = 0, cw = 0.0f;
                     if ((amax >> 7) != 0) {
                         const int maxexp = (int)(amax >> 7) - 127;
