@@ -336,14 +336,17 @@ __global__ void __launch_bounds__(kThreads, TESSL_GEMV_MMA_MIN_BLOCKS) q4_gemv_m
                 if (lane == 0) fail(1, j);
                 break;
             }
-            // A short launch asks for three stages at once and for the rest of its ring once the consumers hold x:
-            // every block's whole ring requested at the block's start put the first stage of a block that starts late
-            // (its SM was the last to finish the previous launch) behind the other blocks' later stages, and the
-            // launch's first MMA waits for that stage. 12288 x 4096 back to back: 7.9 -> 7.2 us, 18992 x 4096 10.0 ->
-            // 9.6 us; a long stream loses the idle start instead (151936 x 4096: 52.4 -> 52.8 us), hence the limit.
-            // Releasing the tail earlier (at the dependency wait's return, or once x is in registers) gave 7.2 us where
-            // this gives 6.8; letting the blocks with the most stages skip the hold changed nothing.
-            if (j == kHoldFrom && n_local <= kHoldMaxStages && !mbar_wait(xbar, 0, abortp, 64)) {
+            // A short launch asks for three stages of its ring at once (one, where a stage holds rows of 8192 or 12288
+            // columns) and for the rest once the consumers hold x. Every block's whole ring requested at the block's
+            // start has two costs: the load of x, issued when the previous launch has ended, returns behind whatever
+            // copies this SM still has in flight, and the first stage of a block that starts late waits behind the
+            // other blocks' later stages. 12288 x 4096 back to back: 7.9 -> 7.2 us, 18992 x 4096 10.0 -> 9.6 us,
+            // 4096 x 12288 8.3 -> 7.8 us; a long stream loses the idle start instead (151936 x 4096: 52.4 -> 52.8 us),
+            // hence the limit. Releasing the tail earlier (at the dependency wait's return, or once x is in registers)
+            // gave 7.2 us where this gives 6.8; two or four stages instead of three were slower (also for Q8, whose
+            // stages are larger: a rule by bytes in flight does not describe it); letting the blocks with the most
+            // stages skip the hold changed nothing.
+            if (j == (NWIN > 1 ? 1u : kHoldFrom) && n_local <= kHoldMaxStages && !mbar_wait(xbar, 0, abortp, 64)) {
                 if (lane == 0) fail(1, j);
                 break;
             }
