@@ -49,7 +49,7 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 HIDDEN, QKV, INTER, GROUP = 4096, 6144, 12288, 64
-TRAFFIC_RATIO = 1.0016  # ncu dram__bytes_read.sum + write.sum over algorithmic bytes, q4_gemv_mma_kernel at 12288 x 4096
+TRAFFIC_RATIO = 1.0014  # ncu dram__bytes_read.sum + write.sum over algorithmic bytes, q4_gemv_mma_kernel at 12288 x 4096
 METRIC = "Q4 GEMV effective weight GB/s"
 
 
