@@ -1,41 +1,45 @@
-// Q4 GEMV / small-batch GEMM (M <= 8, rows of 1024, 2048 or 4096 columns) with
-// the dot products on the tensor cores.
+// Q4 GEMV / small-batch GEMM (M <= 8, rows of 1024, 2048 or 4096 columns; one row of x also over rows of 8192 and
+// 12288 columns) and MLX-layout Q8 (M <= 8), with the dot products on the tensor cores.
 //
 // Why: on the FMA pipe a weight costs one FMA plus 7/8 of a bit-manipulation
 // instruction plus overheads, about 2 issue slots; HBM3e delivers ~46 weights
 // per clock and SM, which would need ~90 of the SM's 128 slots per clock, and
 // the FMA-pipe kernels measured compute-bound at ~30 weights per clock (73% of
-// the memory roofline on a long stream). The nibble -> bf16 step already
-// produces exactly the register layout of an `mma.sync.m16n8k16` A fragment
-// (two bf16 values 128 + q per 32-bit word), so here one MMA replaces 256 FMAs:
-// 16 weight rows x 16 columns against the activations as the B operand, whose 8
-// columns are the up to 8 rows of the batch (for M = 1 all 8 hold the same
-// vector). That is ~1.4 issue slots per weight; the kernel is then bound by the
-// weight stream. The batch rides along for free, so M = 2..8 costs what M = 1
-// costs.
+// the memory roofline on a long stream). A nibble pair masked in place is
+// already the register layout of an `mma.sync.m16n8k16` A fragment: read as bf16
+// bit patterns, 0..15 and 16 x (0..15) are q * 2^-133 exactly (the subnormals and
+// the first binade are one linear scale), and the activations carry the rest
+// (scaled by a power of two, the partners of the odd nibbles by a sixteenth of it).
+// So one MMA replaces 256 FMAs: 16 weight rows x 16 columns against the
+// activations as the B operand, whose 8 columns are the up to 8 rows of the batch
+// (for M = 1 all 8 hold the same vector). The kernel is then bound by the weight
+// stream on a long launch and by its start and the consumers' ALU rate on a short one.
 //
 // Structure (one persistent block per SM, 18 warps):
-//   warp 16   producer: streams row blocks (16 rows of one bank, or 8 + 8 rows of
-//             a gate/up pair) through a ring of stages with plain `cp.async.bulk`
-//             copies, one per PAIR of adjacent rows (each issued by its own lane): the
-//             copy engine's cost is per copy more than per byte (sixteen 2 KB copies per
-//             stage held a long stream to 0.75 of the HBM rate, eight 4 KB copies reach
-//             0.9). The pairs sit 32 bytes past a multiple of 128 apart
-//             (bank-conflict-free reads), and the two rows of a pair are the MMA rows g
-//             and g + 8 that one lane group reads. Plus the rows' scale/bias pairs.
-//             It never waits for the preceding kernel: weights are not written by it.
-//   warps 0-15 consumers: warp w owns columns [w K/16, (w+1) K/16) of every row.
-//             Its activations for that slice stay in registers as B fragments for
-//             the whole launch. Per stage it runs one MMA chain per quantization
-//             group (the chain starts from zero because each group has its own
-//             scale), folds `scale * (dot - 128 xsum) + bias * xsum` in f32 like
-//             the other GEMV kernels, and leaves its partial sums in shared memory.
-//   warp 17   reducer: adds the 16 partial sums of each output in warp order,
-//             applies the epilogue (residual, SiLU/GELU gate) and stores.
+//   warp 16   producer: sets up the barriers, then streams row blocks (16 rows of one
+//             bank, or 8 + 8 rows of a gate/up pair) through a ring of stages with plain
+//             `cp.async.bulk` copies, one per PAIR of adjacent rows or per four rows (each
+//             issued by its own lane): the copy engine's cost is per copy more than per
+//             byte (sixteen 2 KB copies per stage held a long stream to 0.75 of the HBM
+//             rate, eight 4 KB copies reach 0.9, four 8 KB copies the pure read rate). The
+//             pairs sit 32 bytes past a multiple of 128 apart (bank-conflict-free reads),
+//             and the two rows of a pair are the MMA rows g and g + 8 that one lane group
+//             reads. Plus the rows' scale/bias pairs. It never waits for the preceding
+//             kernel (weights are not written by it) nor for the other warps of its block.
+//   warps 0-15 consumers: warp w owns columns [w K/16, (w+1) K/16) of every row (of every
+//             4096-column window of a long row). After the dependency wait it stages its
+//             slice of x once; the B fragments then stay in registers for the whole launch
+//             (long rows: reloaded from the staged copy per window). Per stage it runs one
+//             MMA chain per quantization group (the chain starts from zero because each
+//             group has its own scale), folds `scale * dot + bias * xsum` in f32 like the
+//             reference's qdot16, and leaves its partial sums in shared memory.
+//   warp 17   reducer: adds the 16 partial sums of each output in warp order, applies the
+//             epilogue (residual, SiLU/GELU gate) and stores - in a column-sharded launch
+//             also into every peer GPU's gather buffer, followed by the flag exchange.
 // A row's summation order depends only on K and the group size, so fused
 // gate/up, K/V and Q/K/V launches give the same bits as separate launches.
 //
-// Every mbarrier wait is bounded (see q4_gemv_tma.cuh).
+// Every mbarrier wait and every wait for a peer is bounded (see q4_gemv_tma.cuh).
 #pragma once
 #include <cstddef>
 
@@ -44,9 +48,7 @@
 namespace tessl {
 namespace q4m {
 
-using q4k::and_or;
 using q4k::bulk_g2s;
-using q4k::kMagic;
 using q4k::lds32;
 using q4k::mbar_arrive;
 using q4k::mbar_expect_tx;
