@@ -309,6 +309,9 @@ __global__ void __launch_bounds__(kThreads, TESSL_GEMV_MMA_MIN_BLOCKS) q4_gemv_m
         const uint32_t my_dst = lane < 16 ? pair_off(mg) + mhi * row_bytes
                                           : off_sb + (sb_by_row ? my_r : my_bank * RPB) * sb_row_bytes;
         uint32_t s = 0, ph = 0, issued = 0;
+        // the first stage that waits for x (see the loop); a block of exactly three stages holds its last one
+        // (6144 x 4096: 4.64 -> 4.47 us)
+        const uint32_t hold_from = NWIN > 1 ? 1u : (n_local == 3 ? 2u : kHoldFrom);
         int cur_seg = -1;
         uint32_t seg_end_rb = 0, seg_rows = 0, row0 = 0;
         const uint8_t *src = nullptr;   // this lane's next source: a packed row (lanes 0-15) or the block's scale rows
@@ -348,7 +351,7 @@ __global__ void __launch_bounds__(kThreads, TESSL_GEMV_MMA_MIN_BLOCKS) q4_gemv_m
             // gave 7.2 us where this gives 6.8; two or four stages instead of three were slower (also for Q8, whose
             // stages are larger: a rule by bytes in flight does not describe it); letting the blocks with the most
             // stages skip the hold changed nothing.
-            if (j == (NWIN > 1 ? 1u : kHoldFrom) && n_local <= kHoldMaxStages && !mbar_wait(xbar, 0, abortp, 64)) {
+            if (j == hold_from && n_local <= kHoldMaxStages && !mbar_wait(xbar, 0, abortp, 64)) {
                 if (lane == 0) fail(1, j);
                 break;
             }
