@@ -423,14 +423,16 @@ __global__ void __launch_bounds__(kThreads, TESSL_GEMV_MMA_MIN_BLOCKS) q4_gemv_m
         }
         uint32_t s = 0, ph = 0;
         for (uint32_t j = 0; good && j < n_local; ++j) {
+            // where the stage's outputs go, looked up while the consumers are still at work on it
+            Seg sg;
+            uint32_t row0;
+            locate(rb_lo + j, sg, row0);
+            const float rv = (p.epi == q4k::EPI_ADD_RESID && !BATCH && lane < RPB && row0 + lane < sg.rows) ? sg.resid[row0 + lane] : 0.0f;
             if (!mbar_wait(done(s), ph, abortp, 32)) {
                 if (lane == 0) fail(3, j);
                 good = false;
                 break;
             }
-            Seg sg;
-            uint32_t row0;
-            locate(rb_lo + j, sg, row0);
             const uint32_t part = ring + s * stage_bytes + off_part;
             if constexpr (!BATCH) {
                 // lane r < RPB: output row row0 + r (for a gate/up pair also its up partner, MMA row r + 8)
@@ -448,7 +450,7 @@ __global__ void __launch_bounds__(kThreads, TESSL_GEMV_MMA_MIN_BLOCKS) q4_gemv_m
                     }
                     v = v0;
                     if (p.epi == q4k::EPI_ADD_RESID) {
-                        v = v + sg.resid[row];
+                        v = v + rv;
                     } else if (p.epi == q4k::EPI_GATE_UP_SILU) {
                         v = dev::silu(v0) * v1;
                     } else if (p.epi == q4k::EPI_GATE_UP_GELU) {
