@@ -660,17 +660,24 @@ __global__ void __launch_bounds__(kThreads, TESSL_GEMV_MMA_MIN_BLOCKS) q4_gemv_m
             auto pair = [&](uint32_t lo, uint32_t hi, int ee) { return scaled(lo & 0xffffu, ee) | (scaled(hi & 0xffffu, ee) << 16); };
             if constexpr (!BATCH && !Q8) {
                 constexpr uint32_t NW = 4 * SW;  // 8-column words of the slice: lane L < NW handles word L
+                // Every window's load first, then the processing: one L2 round trip on the launch's start-up path
+                // instead of one per window (the loads are volatile: the compiler would not move them).
+                uint4 rw[NWIN];
 #pragma unroll
                 for (int win = 0; win < NWIN; ++win) {
-                    const uint32_t xst = xstage + win * kXStageBytes;
-                    uint4 r = make_uint4(0u, 0u, 0u, 0u);
+                    rw[win] = make_uint4(0u, 0u, 0u, 0u);
                     // a coherent load: x may be a gather buffer that a peer GPU filled while this kernel was waiting
                     if ((uint32_t)lane < NW) {
                         asm volatile("ld.global.v4.u32 {%0,%1,%2,%3}, [%4];"
-                                     : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w)
+                                     : "=r"(rw[win].x), "=r"(rw[win].y), "=r"(rw[win].z), "=r"(rw[win].w)
                                      : "l"(xrow + win * KW + k0 + 8 * lane)
                                      : "memory");
                     }
+                }
+#pragma unroll
+                for (int win = 0; win < NWIN; ++win) {
+                    const uint32_t xst = xstage + win * kXStageBytes;
+                    const uint4 r = rw[win];
                     uint32_t amax = max(max(r.x & 0x7fffu, (r.x >> 16) & 0x7fffu), max(r.y & 0x7fffu, (r.y >> 16) & 0x7fffu));
                     amax = max(amax, max(max(r.z & 0x7fffu, (r.z >> 16) & 0x7fffu), max(r.w & 0x7fffu, (r.w >> 16) & 0x7fffu)));
                     amax = __reduce_max_sync(0xffffffffu, amax);  // one instruction: this chain is the launch's start-up path
