@@ -455,9 +455,12 @@ bool launch_mma_windows(TesslRuntime *rt, const Q4GemvParams &p, int m, int nb, 
 template <int SW, int WPG>
 Result launch_mma_q8_sw(TesslRuntime *rt, const Q4GemvParams &p, int m)
 {
-    // 4096 codes per row: a 16-row stage with the batch's partial sums is 77 KB and only two fit; 8-row stages
-    // (half of each MMA idle, which this format can afford: one MMA per 8 bytes of weights) give five.
-    if (SW == 16 && m > 1) return launch_mma_one<SW, WPG, 1, true, true, 1, 8>(rt, p, m);
+    // 4096 codes per row: a 16-row stage with the batch's partial sums is 77 KB and only two fit; 10-row stages
+    // (part of each MMA idle, which this format can afford: one MMA per 8 bytes of weights) give four. A stage's
+    // compute does not depend on its height, so fewer and taller stages win as long as the ring stays deep enough:
+    // 14336 x 4096 at M = 2 / 4 / 8: 8 rows (five stages) 16.5 / 17.0 / 17.5 us, 10 rows 14.6 / 15.0 / 15.6 us,
+    // 12 rows (three stages) 16.8 / 17.1 / 17.7 us.
+    if (SW == 16 && m > 1) return launch_mma_one<SW, WPG, 1, true, true, 1, 10>(rt, p, m);
     if (SW == 16 && m == 1) {
         // One row of x over 4096 codes per row is bound by the stream, not by the consumers (a stage's compute does
         // not depend on its height, its bytes do), so the stage height that leaves the shortest tail wins: the
